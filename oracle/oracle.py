@@ -1,0 +1,170 @@
+"""CPU oracle for the side-aware elementwise path.  TEST INFRASTRUCTURE ONLY.
+
+Three layers, each checked against the next one down:
+
+* numpy restatements (this file) - small, readable, vectorised;
+* ``liboracle.so`` - the C restatement in ``rope_oracle.c`` (fast enough for the
+  full benchmark shapes, also the timed CPU baseline);
+* ``_ref/libref_rope.so`` - the reference's own CPU code compiled in place
+  (``ref_shim.cu``); present wherever the reference tree was available at
+  build time.
+
+Parity status: PINNED (restatements == compiled reference == committed golden
+vectors under ``tests/golden``).
+
+Nothing in the shipped package imports this module.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_REF = None
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+
+
+def _ptr(a, ty):
+    return a.ctypes.data_as(ty)
+
+
+def build(force: bool = False) -> None:
+    """Compile liboracle.so (and _ref/ when the reference tree is present)."""
+    if force or not os.path.exists(os.path.join(_HERE, "liboracle.so")) or (
+        os.path.getmtime(os.path.join(_HERE, "liboracle.so")) < os.path.getmtime(os.path.join(_HERE, "rope_oracle.c"))
+    ):
+        subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
+    ref_src = os.environ.get("SIDEAWARE_REFERENCE_TREE", "/root/reference")
+    if os.path.exists(os.path.join(ref_src, "example_llmc_rope.cu")) and (
+        force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_rope.so"))
+    ):
+        subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={ref_src}"], stdout=subprocess.DEVNULL)
+
+
+def lib() -> ctypes.CDLL:
+    """The C restatement."""
+    global _LIB
+    if _LIB is None:
+        build()
+        L = ctypes.CDLL(os.path.join(_HERE, "liboracle.so"))
+        L.oracle_precompute_freqs_cis.argtypes = [_f32p, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int]
+        L.oracle_rope_forward_f32.argtypes = [_f32p, _f32p, _f32p] + [ctypes.c_int] * 5
+        L.oracle_rope_forward_bf16.argtypes = [_u16p, _u16p, _f32p] + [ctypes.c_int] * 5
+        L.oracle_silu_mul_bf16.argtypes = [_u16p, _u16p, _u16p, ctypes.c_float, ctypes.c_size_t]
+        L.oracle_memcpy_mt.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+        L.oracle_rope_forward_mt.argtypes = [ctypes.c_void_p, ctypes.c_void_p, _f32p] + [ctypes.c_int] * 7
+        L.oracle_bf16_to_f32.argtypes = [_f32p, _u16p, ctypes.c_size_t]
+        L.oracle_f32_to_bf16.argtypes = [_u16p, _f32p, ctypes.c_size_t]
+        for f in ("oracle_precompute_freqs_cis", "oracle_rope_forward_f32", "oracle_rope_forward_bf16",
+                  "oracle_silu_mul_bf16", "oracle_memcpy_mt", "oracle_rope_forward_mt",
+                  "oracle_bf16_to_f32", "oracle_f32_to_bf16"):
+            getattr(L, f).restype = None
+        _LIB = L
+    return _LIB
+
+
+def ref_available() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "libref_rope.so"))
+
+
+def ref() -> ctypes.CDLL:
+    """The compiled reference (its CPU functions only are ever called)."""
+    global _REF
+    if _REF is None:
+        path = os.path.join(_HERE, "_ref", "libref_rope.so")
+        try:
+            R = ctypes.CDLL(path)
+        except OSError:
+            # No GPU driver on this machine: satisfy the libcuda.so.1 dependency with
+            # the toolkit's link stub (none of its entry points are called).
+            stub = "/usr/local/cuda/lib64/stubs/libcuda.so"
+            ctypes.CDLL(stub, mode=ctypes.RTLD_GLOBAL)
+            R = ctypes.CDLL(path)
+        R.ref_precompute_freqs_cis.argtypes = [_f32p, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int]
+        R.ref_precompute_freqs_cis.restype = None
+        R.ref_apply_rotary_emb_forward.argtypes = [_f32p, _f32p, _f32p] + [ctypes.c_int] * 4
+        R.ref_apply_rotary_emb_forward.restype = None
+        _REF = R
+    return _REF
+
+
+# ---------------------------------------------------------------------------
+# C restatement wrappers
+# ---------------------------------------------------------------------------
+def freqs_cis(dim: int, end: int, theta: float, use_scaled: int = 0) -> np.ndarray:
+    """[end, dim/2, 2] fp32 cos/sin table (example_llmc_rope.cu:19-52)."""
+    t = np.empty((end, dim // 2, 2), dtype=np.float32)
+    lib().oracle_precompute_freqs_cis(_ptr(t, _f32p), dim, end, theta, use_scaled)
+    return t
+
+
+def rope_forward_f32(inp: np.ndarray, table: np.ndarray, B, T, Nq, Nkv, HS) -> np.ndarray:
+    inp = np.ascontiguousarray(inp, dtype=np.float32)
+    table = np.ascontiguousarray(table, dtype=np.float32)
+    out = np.empty_like(inp)
+    lib().oracle_rope_forward_f32(_ptr(out, _f32p), _ptr(inp, _f32p), _ptr(table, _f32p), B, T, Nq, Nkv, HS)
+    return out
+
+
+def rope_forward_bf16(inp_u16: np.ndarray, table: np.ndarray, B, T, Nq, Nkv, HS, threads: int = 1) -> np.ndarray:
+    """bf16 bit patterns in and out (uint16 arrays)."""
+    inp_u16 = np.ascontiguousarray(inp_u16, dtype=np.uint16)
+    table = np.ascontiguousarray(table, dtype=np.float32)
+    out = np.empty_like(inp_u16)
+    if threads > 1:
+        lib().oracle_rope_forward_mt(out.ctypes.data, inp_u16.ctypes.data, _ptr(table, _f32p), B, T, Nq, Nkv, HS, 1, threads)
+    else:
+        lib().oracle_rope_forward_bf16(_ptr(out, _u16p), _ptr(inp_u16, _u16p), _ptr(table, _f32p), B, T, Nq, Nkv, HS)
+    return out
+
+
+def silu_mul_bf16(a_u16: np.ndarray, b_u16: np.ndarray, scale: float) -> np.ndarray:
+    a_u16 = np.ascontiguousarray(a_u16, dtype=np.uint16)
+    b_u16 = np.ascontiguousarray(b_u16, dtype=np.uint16)
+    out = np.empty_like(a_u16)
+    lib().oracle_silu_mul_bf16(_ptr(out, _u16p), _ptr(a_u16, _u16p), _ptr(b_u16, _u16p), scale, a_u16.size)
+    return out
+
+
+def bf16_to_f32(u16: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(u16, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(f: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(f, dtype=np.float32).view(np.uint32)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    r[nan] = 0x7FFF
+    return r
+
+
+# ---------------------------------------------------------------------------
+# numpy restatements (independent of the C code; used to cross-check it)
+# ---------------------------------------------------------------------------
+def np_rope_forward_f32(inp: np.ndarray, table: np.ndarray, B, T, Nq, Nkv, HS) -> np.ndarray:
+    """Same arithmetic as example_llmc_rope.cu:54-86 with separate fp32 roundings."""
+    heads = Nq + 2 * Nkv
+    x = np.ascontiguousarray(inp, dtype=np.float32).reshape(B, T, heads, HS // 2, 2)
+    tab = np.ascontiguousarray(table, dtype=np.float32).reshape(T, HS // 2, 2)
+    c = tab[None, :, None, :, 0]
+    s = tab[None, :, None, :, 1]
+    out = x.copy()
+    r = Nq + Nkv
+    xr, xi = x[:, :, :r, :, 0], x[:, :, :r, :, 1]
+    out[:, :, :r, :, 0] = (xr * c).astype(np.float32) - (xi * s).astype(np.float32)
+    out[:, :, :r, :, 1] = (xr * s).astype(np.float32) + (xi * c).astype(np.float32)
+    return out.reshape(inp.shape)
+
+
+def ulp_diff_bf16(a_u16: np.ndarray, b_u16: np.ndarray) -> np.ndarray:
+    """Distance in bf16 units of last place between two bit-pattern arrays."""
+    def key(u):
+        u = u.astype(np.int32)
+        return np.where(u & 0x8000, 0x8000 - u, u)
+    return np.abs(key(a_u16) - key(b_u16))
