@@ -1,0 +1,171 @@
+/*
+ * sideaware.h - C ABI of sideaware.so, the B200 (sm_100a) side-aware allocator
+ * and elementwise-kernel library.
+ *
+ * Every entry point of the first section keeps the name, argument meaning and
+ * error behaviour of the corresponding `extern "C"` function of the reference
+ * project (ademeure/l2_torch_alloc, file sideaware.cu; the line each one
+ * replaces is cited).  Streams are passed as opaque pointers (a cudaStream_t),
+ * status codes are CUDA runtime error numbers (0 = success, 2 = out of memory).
+ * No C++ or torch types cross this boundary.
+ *
+ * Thread safety: all entry points may be called from any host thread; state is
+ * guarded per device.  Launchers enqueue on the given stream and return.
+ */
+#ifndef SIDEAWARE_H
+#define SIDEAWARE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* sideaware_stream_t; /* cudaStream_t */
+typedef int sideaware_status_t;   /* cudaError_t value */
+
+/* ---- allocation (replaces sideaware.cu:1280-1352) ------------------------- */
+/* Side-aware block on the current device: 2 MiB granular, VA bit 21 of every
+ * page equals the L2 side its physical page is homed on, same size => same
+ * bit-21 phase.  Replaces sideaware_malloc_async, sideaware.cu:1280. */
+sideaware_status_t sideaware_malloc_async(void** dev_ptr, size_t size, sideaware_stream_t stream);
+/* Returns the block to the (still mapped) reuse cache.  sideaware.cu:1286. */
+sideaware_status_t sideaware_free_async(void* ptr, sideaware_stream_t stream);
+/* Same, after a device synchronisation.  sideaware.cu:1292, :1301. */
+sideaware_status_t sideaware_malloc(void** dev_ptr, size_t size);
+sideaware_status_t sideaware_free(void* ptr);
+/* Unmaps every cached block and releases all pooled physical pages on every
+ * initialised device; returns the bytes released.  sideaware.cu:1307. */
+size_t sideaware_release_unused(void);
+/* PyTorch CUDAPluggableAllocator entry points.  size >= threshold (8 MiB by
+ * default) is served side-aware, smaller sizes by cudaMallocAsync; NULL on
+ * failure.  sideaware.cu:1320, :1343. */
+void* sideaware_malloc_auto(size_t size, int device, sideaware_stream_t stream);
+void sideaware_free_auto(void* ptr, size_t size, int device, sideaware_stream_t stream);
+
+/* ---- kernels (replaces sideaware.cu:1358-1416) ---------------------------- */
+/* Up to 4 outputs / 4 inputs, num_bytes = byte size of the widest array
+ * (multiple of 16; pointers 16-byte aligned).  kernel_id 0 is memcpy.
+ * parallel_groups: 256-thread groups per SM (0 = default), forced_per_side:
+ * limit the SMs used per side (0 = all).  sideaware.cu:1358. */
+void sideaware_elementwise(int kernel_id, size_t num_bytes,
+                           void* out0, void* out1, void* out2, void* out3,
+                           const void* in0, const void* in1, const void* in2, const void* in3,
+                           void* sideband_memory, int sideband_value,
+                           int parallel_groups, int forced_per_side,
+                           int device, sideaware_stream_t stream);
+/* sideaware.cu:1410 */
+void sideaware_one_to_one(int kernel_id, size_t num_bytes, void* out0, const void* in0,
+                          int device, sideaware_stream_t stream);
+/* sideaware.cu:1414 */
+void sideaware_memcpy(void* out, const void* in, size_t num_bytes, int device, sideaware_stream_t stream);
+
+/* ---- user functors (replaces sideaware.cu:1421-1462) ---------------------- */
+/* Registers a functor header (source text following the reference's header
+ * contract, sideaware.cu:81-138) and returns its id; NULL/"" -> 0 (memcpy);
+ * the same text always returns the same id.  Compiled with NVRTC for sm_100a
+ * on first use per device, or immediately when precompile is set.
+ * Returns -1 on a compile error (see sideaware_last_error). */
+int sideaware_create_kernel_advanced(const char* header, bool precompile, int default_num_groups);
+int sideaware_create_kernel(const char* header);
+
+/* ---- configuration (replaces sideaware.cu:1467-1487) ---------------------- */
+void sideaware_compression(bool enable);
+void sideaware_alloc_threshold(size_t threshold);
+void sideaware_prealloc_config(int extra_required, int extra_alloc);
+void sideaware_free_mapped_thresholds(size_t start_threshold, size_t end_threshold);
+/* The reference appends a disassembly of each JIT-ed kernel to this file; this
+ * library appends the NVRTC log and the generated source instead. */
+void sideaware_write_sass(const char* filename);
+
+/* ---- queries (replaces sideaware.cu:1492-1522) ---------------------------- */
+void sideaware_fill_side_index(unsigned char* gpu_array); /* num_sms bytes, device to device */
+const char* sideaware_gpu_side_index(void);               /* device pointer, library owned */
+const char* sideaware_cpu_side_index(void);               /* host pointer: byte = side | ordinal<<1 */
+const int* sideaware_sm_side_summary(void);               /* {num_sms, side0, side1, min, hash|1<<21} */
+int sideaware_num_sms(void);
+int sideaware_num_sm_side0(void);
+int sideaware_num_sm_side1(void);
+int sideaware_min_sm_per_side(void);
+int sideaware_hash_mask(void);
+
+/* =========================================================================
+ * Additions (no counterpart in the reference unless noted).
+ * ========================================================================= */
+
+/* Last error text recorded on the calling thread's most recent failing call
+ * ("" if none).  The reference reports misuse through assert() only
+ * (sideaware.cu:1371-1375); the launchers here stay void and record instead. */
+const char* sideaware_last_error(void);
+/* Number of errors recorded since load (all threads). */
+unsigned long long sideaware_error_count(void);
+
+/* In-place forward RoPE over a packed [B, T, Nq + 2*Nkv, HS] tensor with an
+ * fp32 [T, HS/2, 2] cos/sin table; V heads are not touched.  dtype: 0 = fp32,
+ * 1 = bf16 (fp32 math, one round-to-nearest-even).  Generalises the reference's
+ * fixed-shape functor kernel_rope.cuh:19-60 (MHA, fp32, T=1024) to runtime
+ * shapes; arithmetic is that of example_llmc_rope.cu:54-86 without FMA
+ * contraction.  Returns 0 or a CUDA error number. */
+sideaware_status_t sideaware_rope_forward(void* qkv, const float* freqs_cis,
+                                          int B, int T, int Nq, int Nkv, int HS, int dtype,
+                                          int device, sideaware_stream_t stream);
+
+/* out = bf16(a * sigmoid(a) * b * scale), n elements (multiple of 8), the
+ * ahead-of-time build of the benchmark's example functor. */
+sideaware_status_t sideaware_silu_mul_bf16(void* out, const void* a, const void* b, float scale,
+                                           size_t n, int device, sideaware_stream_t stream);
+
+/* Compiles a functor header with NVRTC for sm_100a without loading it, so headers
+ * can be checked on a machine without a GPU.  wide != 0 selects the 64-bit index
+ * variant.  Returns 0 on success; the compiler log is copied to log_out. */
+int sideaware_compile_check(const char* header, int wide, char* log_out, size_t log_capacity);
+
+/* Kernel placement policy for all launchers: 0 = side-aware (default),
+ * 1 = side-unaware (same kernel, chunk halves chosen without looking at the
+ * address), 2 = forced wrong side.  For A/B measurements; the reference offers
+ * the same through the FORCE_WRONG_SIDE / FORCE_RANDOM_SIDE functor macros
+ * (sideaware.cu:70-75). */
+void sideaware_set_placement(int mode);
+int sideaware_get_placement(void);
+/* memcpy engine: 0 = 128-bit vector loads/stores, 1 = bulk-copy (TMA) staging
+ * through shared memory. */
+void sideaware_set_memcpy_engine(int engine);
+
+/* Per-chunk side map: writes one byte (0/1) per 4 KiB chunk of
+ * [ptr, ptr + num_bytes) to host memory, as predicted from the address hash
+ * and VA bit 21.  Returns the number of chunks written. */
+size_t sideaware_chunk_sides(const void* ptr, size_t num_bytes, unsigned char* host_out);
+/* Re-measures, by L2 latency probing on the GPU, the side of `samples` randomly
+ * chosen chunks of a live allocation and compares with the prediction.
+ * Contents are not modified (atomic add of zero).  Returns the number of
+ * mismatches, or -1 on error. */
+int sideaware_verify_chunk_sides(const void* ptr, size_t num_bytes, int samples, unsigned seed);
+
+/* Counters of the current device, for tests and monitoring. */
+typedef struct sideaware_stats_t {
+    unsigned long long bytes_mapped_live;   /* side-aware blocks handed out */
+    unsigned long long bytes_mapped_cached; /* freed but still mapped */
+    unsigned long long pages_pool_side0;    /* unmapped physical pages */
+    unsigned long long pages_pool_side1;
+    unsigned long long pages_created;       /* cuMemCreate successes since start */
+    unsigned long long cross_side_pages;    /* pages mapped against their side */
+    unsigned long long reuse_hits;
+    unsigned long long large_allocs;
+    unsigned long long small_allocs;        /* served by cudaMallocAsync */
+    unsigned long long trims;               /* threshold/OOM unmap passes */
+    unsigned long long jit_compiles;
+    unsigned long long kernel_launches;
+    unsigned long long probe_confidence_ppm; /* min SM signature margin, 1e6 = perfect */
+    unsigned long long hash_validation_errors; /* mispredicted validation offsets at init */
+} sideaware_stats_t;
+void sideaware_get_stats(sideaware_stats_t* out);
+
+/* Raw discovery data of the current device (latency matrix etc.) as JSON text
+ * owned by the library; for diagnostics. */
+const char* sideaware_topology_json(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIDEAWARE_H */

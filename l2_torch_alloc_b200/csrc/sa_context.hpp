@@ -1,0 +1,73 @@
+// Per-device state of the library and the process-wide configuration.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "sa_alloc.hpp"
+#include "sa_driver.hpp"
+#include "sa_probe.hpp"
+
+struct SaJitDeviceCache; // sa_jit.cpp
+
+struct SaConfig {
+    std::mutex mu;
+    SaAllocConfig alloc;
+    size_t threshold = 8ull << 20; // sizes below go to cudaMallocAsync in the *_auto entry points
+    std::string log_file;          // JIT log destination ("" = none)
+    std::atomic<int> placement{0};
+    std::atomic<int> memcpy_engine{0};
+};
+SaConfig& sa_config();
+
+struct SaDevice {
+    int id = -1;
+    std::mutex mu;
+    bool ready = false, failed = false;
+    std::string fail_why;
+    const SaDriver* drv = nullptr;
+    SaTopology topo;
+    SaProbeDevice* probe = nullptr;
+    uint64_t probe_page_va = 0;
+    unsigned long long probe_page_handle = 0;
+    cudaStream_t probe_stream = nullptr;
+    bool compression_supported = false;
+    std::unique_ptr<SaBackend> backend;
+    std::unique_ptr<SaAllocator> alloc;
+    int summary[5] = {0, 0, 0, 0, 0};
+    uint32_t full_hash = 0; // hash | 1 << 21 when usable, else 0
+    std::atomic<unsigned long long> small_allocs{0}, launches{0}, jit_compiles{0};
+    SaJitDeviceCache* jit = nullptr;
+    std::mutex jit_mu;
+    ~SaDevice();
+};
+
+// Device `device` (< 0: the calling thread's current device), initialised on first use.
+// nullptr after recording an error when the device cannot be set up.
+SaDevice* sa_device(int device);
+// Every device that has been initialised so far.
+std::vector<SaDevice*> sa_initialised_devices();
+
+// Makes `device` current for the lifetime of the object, then restores the previous one.
+class SaScopedDevice {
+public:
+    explicit SaScopedDevice(int device);
+    ~SaScopedDevice();
+private:
+    int prev_ = -1;
+    bool switched_ = false;
+};
+
+// Error channel: text kept per thread, count kept per process, line written to stderr.
+void sa_set_error(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+const char* sa_last_error_text();
+unsigned long long sa_error_total();
+
+// Fills the launch-constant scheduling state for an array of `num_vecs` 16-byte vectors
+// whose side-tracking array starts at `track_addr`, and picks grid and block size.
+void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
+                       int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads);

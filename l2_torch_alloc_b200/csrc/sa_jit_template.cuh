@@ -1,0 +1,200 @@
+// Generic side-aware elementwise kernel for user functors, compiled at run time
+// with NVRTC for sm_100a.  The text of this file is embedded in the library and
+// appended after (1) a small prefix generated per device and variant, (2) the
+// user's functor header and (3) sa_sched.cuh.
+//
+// Functor header contract (kept from the reference, sideaware.cu:60-138):
+//   typedef ... o0, o1, o2, o3, i0, i1, i2, i3;      unused slots are `unused` (struct unused {};)
+//   constexpr bool reverse_order;                     walk the array from the end
+//   constexpr bool input_evict[4];                    stream (evict-first) loads per input
+//   __device__ void elementwise_op(size_t idx, int sideband, o0&, o1&, o2&, o3&,
+//                                  const i0&, const i1&, const i2&, const i3&);
+//   optional macros: UNROLLED, LAUNCH_BOUNDS, DISCARD_INPUTS (+ constexpr bool input_discard[4]),
+//   CUSTOM_VECTOR_OP (+ vector_op), CUSTOM_IDX_FUNC (+ indexing), FORCE_WRONG_SIDE,
+//   FORCE_RANDOM_SIDE, DYNAMIC_INDEX_FOR_CONCURRENT_KERNELS (accepted; work
+//   assignment here is always dynamic).
+// The prefix provides size_type, aligned_2MiB, MAX_SM and HASH as the reference does
+// (sideaware.cu:786-795).
+//
+// The widest array (i0, or o0 if its element is larger) is moved as 16-byte
+// vectors; the others move vec_size elements per vector with 16/8/4/2/1-byte
+// accesses.  A warp owns one 4 KiB chunk of the widest array at a time and
+// processes it in batches of UNROLLED vectors per lane: all loads of a batch
+// are issued before its arithmetic and stores.
+
+#ifndef UNROLLED
+#define UNROLLED 4
+#endif
+#ifndef LAUNCH_BOUNDS
+#define LAUNCH_BOUNDS __launch_bounds__(1024, 1)
+#endif
+#ifndef DISCARD_INPUTS
+constexpr bool input_discard[4] = {false, false, false, false};
+#endif
+#ifndef FORCE_WRONG_SIDE
+#define FORCE_WRONG_SIDE false
+#endif
+#ifndef FORCE_RANDOM_SIDE
+#define FORCE_RANDOM_SIDE false
+#endif
+
+constexpr int sa_batch = (UNROLLED) >= 8 ? 8 : (UNROLLED) >= 4 ? 4 : (UNROLLED) >= 2 ? 2 : 1;
+constexpr bool sideaware_for_o0 = sizeof(o0) > sizeof(i0);
+constexpr int vec_size = 16 / (int)(sideaware_for_o0 ? sizeof(o0) : sizeof(i0));
+
+template <typename A, typename B> struct sa_same { static constexpr bool value = false; };
+template <typename A> struct sa_same<A, A> { static constexpr bool value = true; };
+template <typename T> constexpr bool sa_used = !sa_same<T, unused>::value;
+
+// vec_size elements of T, aligned so one access moves them when the size allows it
+template <typename T, int BYTES = (int)sizeof(T) * vec_size>
+struct alignas(BYTES == 16 || BYTES == 8 || BYTES == 4 || BYTES == 2 ? BYTES : alignof(T)) sa_pack {
+    T v[vec_size];
+};
+
+#ifndef CUSTOM_VECTOR_OP
+__device__ __forceinline__ void vector_op(size_type vec_idx, int n,
+                                          o0* out0, o1* out1, o2* out2, o3* out3,
+                                          const i0* in0, const i1* in1, const i2* in2, const i3* in3,
+                                          int* sideband_memory, int sideband_value) {
+#pragma unroll
+    for (int e = 0; e < n; ++e)
+        elementwise_op((size_t)vec_idx * n + e, sideband_value, out0[e], out1[e], out2[e], out3[e],
+                       in0[e], in1[e], in2[e], in3[e]);
+}
+#endif
+
+#ifndef CUSTOM_IDX_FUNC
+__device__ __forceinline__ bool indexing(size_type vec_idx, int n, size_type& idx_i0, size_type& idx_i1,
+                                         size_type& idx_i2, size_type& idx_i3, int* sideband_memory, int sideband_value) {
+    idx_i0 = idx_i1 = idx_i2 = idx_i3 = vec_idx;
+    return false;
+}
+#endif
+
+template <bool EVICT, typename T>
+__device__ __forceinline__ void sa_load(sa_pack<T>& dst, const sa_pack<T>* base, size_type idx) {
+    if constexpr (sa_used<T>) {
+        const sa_pack<T>* p = base + idx;
+        if constexpr (sizeof(sa_pack<T>) == 16) {
+            int4 r = EVICT ? __ldcs((const int4*)p) : __ldcg((const int4*)p);
+            *(int4*)&dst = r;
+        } else if constexpr (sizeof(sa_pack<T>) == 8) {
+            int2 r = EVICT ? __ldcs((const int2*)p) : __ldcg((const int2*)p);
+            *(int2*)&dst = r;
+        } else if constexpr (sizeof(sa_pack<T>) == 4) {
+            int r = EVICT ? __ldcs((const int*)p) : __ldcg((const int*)p);
+            *(int*)&dst = r;
+        } else if constexpr (sizeof(sa_pack<T>) == 2) {
+            short r = EVICT ? __ldcs((const short*)p) : __ldcg((const short*)p);
+            *(short*)&dst = r;
+        } else {
+            dst = *p;
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void sa_store(sa_pack<T>* base, size_type idx, const sa_pack<T>& v) {
+    if constexpr (sa_used<T>) {
+        sa_pack<T>* p = base + idx;
+        if constexpr (sizeof(sa_pack<T>) == 16) *(int4*)p = *(const int4*)&v;
+        else if constexpr (sizeof(sa_pack<T>) == 8) *(int2*)p = *(const int2*)&v;
+        else if constexpr (sizeof(sa_pack<T>) == 4) *(int*)p = *(const int*)&v;
+        else if constexpr (sizeof(sa_pack<T>) == 2) *(short*)p = *(const short*)&v;
+        else *p = v;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void sa_discard(const sa_pack<T>* base, size_type idx, bool enabled) {
+    if constexpr (sa_used<T>) {
+        const sa_pack<T>* p = base + idx;
+        // drops a whole 128-byte line from L2 without writing it back: only lines the kernel has consumed
+        if (enabled && ((unsigned long long)p & 127ull) == 0) asm volatile("discard.global.L2 [%0], 128;" ::"l"(p) : "memory");
+    }
+}
+
+struct SaJitArgs {
+    size_type num_vecs;
+    void* out[4];
+    const void* in[4];
+    int* mem;
+    int val;
+};
+
+extern "C" __global__ LAUNCH_BOUNDS void sideaware_elementwise(const __grid_constant__ SaSched launch,
+                                                               const __grid_constant__ SaJitArgs a) {
+    // geometry follows the array that is moved in 16-byte vectors
+    SaSched s = launch;
+    sa_sched_geometry(s, (sa_u64)(sideaware_for_o0 ? a.out[0] : a.in[0]), (sa_u64)a.num_vecs, 0);
+    s.reverse = reverse_order ? 1u : 0u;
+    if (FORCE_WRONG_SIDE && s.hash) s.placement = SA_PLACE_WRONG;
+    if (FORCE_RANDOM_SIDE) s.placement = SA_PLACE_UNAWARE;
+
+    sa_pack<o0>* const po0 = (sa_pack<o0>*)a.out[0];
+    sa_pack<o1>* const po1 = (sa_pack<o1>*)a.out[1];
+    sa_pack<o2>* const po2 = (sa_pack<o2>*)a.out[2];
+    sa_pack<o3>* const po3 = (sa_pack<o3>*)a.out[3];
+    const sa_pack<i0>* const pi0 = (const sa_pack<i0>*)a.in[0];
+    const sa_pack<i1>* const pi1 = (const sa_pack<i1>*)a.in[1];
+    const sa_pack<i2>* const pi2 = (const sa_pack<i2>*)a.in[2];
+    const sa_pack<i3>* const pi3 = (const sa_pack<i3>*)a.in[3];
+    const sa_u32 lane = sa_lane();
+
+    sa_for_each_chunk(s, [&](sa_u64 first_vec) {
+        const bool whole = first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end;
+#pragma unroll 1
+        for (int b = 0; b < SA_VEC_PER_LANE / sa_batch; ++b) {
+            size_type vidx[sa_batch];
+            size_type ix[sa_batch][4];
+            bool live[sa_batch];
+            sa_pack<i0> r0[sa_batch];
+            sa_pack<i1> r1[sa_batch];
+            sa_pack<i2> r2[sa_batch];
+            sa_pack<i3> r3[sa_batch];
+#pragma unroll
+            for (int j = 0; j < sa_batch; ++j) {
+                sa_u64 v = first_vec + (sa_u64)(b * sa_batch + j) * 32u + lane;
+                live[j] = whole || (v >= s.lead && v < s.end);
+                vidx[j] = (size_type)(v - s.lead);
+                if (live[j]) {
+                    ix[j][0] = ix[j][1] = ix[j][2] = ix[j][3] = 0;
+                    bool skip = indexing(vidx[j], vec_size, ix[j][0], ix[j][1], ix[j][2], ix[j][3], a.mem, a.val);
+                    live[j] = !skip;
+                }
+                if (live[j]) {
+                    sa_load<input_evict[0]>(r0[j], pi0, ix[j][0]);
+                    sa_load<input_evict[1]>(r1[j], pi1, ix[j][1]);
+                    sa_load<input_evict[2]>(r2[j], pi2, ix[j][2]);
+                    sa_load<input_evict[3]>(r3[j], pi3, ix[j][3]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < sa_batch; ++j) {
+                if (live[j]) {
+                    sa_pack<o0> w0;
+                    sa_pack<o1> w1;
+                    sa_pack<o2> w2;
+                    sa_pack<o3> w3;
+                    vector_op(vidx[j], vec_size, w0.v, w1.v, w2.v, w3.v, r0[j].v, r1[j].v, r2[j].v, r3[j].v, a.mem, a.val);
+                    sa_store(po0, vidx[j], w0);
+                    sa_store(po1, vidx[j], w1);
+                    sa_store(po2, vidx[j], w2);
+                    sa_store(po3, vidx[j], w3);
+                }
+            }
+#ifdef DISCARD_INPUTS
+#pragma unroll
+            for (int j = 0; j < sa_batch; ++j) {
+                if (live[j]) {
+                    sa_discard(pi0, ix[j][0], input_discard[0]);
+                    sa_discard(pi1, ix[j][1], input_discard[1]);
+                    sa_discard(pi2, ix[j][2], input_discard[2]);
+                    sa_discard(pi3, ix[j][3], input_discard[3]);
+                }
+            }
+#endif
+        }
+    });
+}

@@ -1,0 +1,212 @@
+// Ahead-of-time side-aware kernels for sm_100a: memcpy, in-place forward RoPE
+// (fp32 and bf16 storage) and the bf16 silu-mul example functor.
+//
+// Every kernel is a persistent grid of one 1024-thread block per SM.  A warp
+// owns one 4 KiB chunk at a time: 32 lanes x 16 bytes per instruction, eight
+// independent 128-bit loads in flight per lane, then the arithmetic, then
+// eight 128-bit stores.  Which chunks a warp takes is decided by sa_sched.cuh.
+// None of these paths is a contraction, so no tensor-core instructions appear;
+// the bound is HBM bandwidth.
+//
+// Replaces the reference's JIT-ed template kernel for these functors:
+// sideaware.cu:194-386 with the memcpy header sideaware.cu:33-48 and the RoPE
+// header kernel_rope.cuh:1-60.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "sa_kernels.hpp"
+
+namespace {
+
+constexpr int kMaxThreads = 1024;
+
+// streaming (evict-first) 128-bit load: the data is used once
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+
+// ---------------------------------------------------------------------------
+// memcpy
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kMaxThreads, 1)
+sa_memcpy_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ dst, const uint4* __restrict__ src) {
+    const uint32_t lane = sa_lane();
+    sa_for_each_chunk(s, [&](uint64_t first_vec) {
+        if (first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end) {
+            const uint64_t e = first_vec - s.lead + lane;
+            const uint4* p = src + e;
+            uint4 r[SA_VEC_PER_LANE];
+#pragma unroll
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) r[k] = ld_stream(p + k * 32);
+            uint4* q = dst + e;
+#pragma unroll
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) q[k * 32] = r[k];
+        } else {
+            // first or last chunk of the array: per-vector bounds
+#pragma unroll 1
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                uint64_t v = first_vec + k * 32 + lane;
+                if (v >= s.lead && v < s.end) dst[v - s.lead] = ld_stream(src + (v - s.lead));
+            }
+        }
+    });
+}
+
+// ---------------------------------------------------------------------------
+// RoPE forward, in place on packed [B, T, Nq + 2 Nkv, HS]
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void rotate(float x, float y, float c, float s, float& ox, float& oy) {
+    // separate roundings, no fused multiply-add: identical to the host arithmetic of
+    // example_llmc_rope.cu:80-81 compiled without contraction
+    ox = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s));
+    oy = __fadd_rn(__fmul_rn(x, s), __fmul_rn(y, c));
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab) {
+    uint4 out;
+    if constexpr (BF16) {
+        // 8 bf16 = 4 pairs, table = 4 x (cos, sin) = two float4
+        const float4 t0 = __ldg(tab), t1 = __ldg(tab + 1);
+        const float cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            float x = __uint_as_float(w[p] << 16), y = __uint_as_float(w[p] & 0xffff0000u);
+            float ox, oy;
+            rotate(x, y, cs[2 * p], cs[2 * p + 1], ox, oy);
+            __nv_bfloat162 b = __floats2bfloat162_rn(ox, oy);
+            o[p] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        out = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+        // 4 floats = 2 pairs, table = one float4
+        const float4 t = __ldg(tab);
+        float ox0, oy0, ox1, oy1;
+        rotate(__uint_as_float(in.x), __uint_as_float(in.y), t.x, t.y, ox0, oy0);
+        rotate(__uint_as_float(in.z), __uint_as_float(in.w), t.z, t.w, ox1, oy1);
+        out = make_uint4(__float_as_uint(ox0), __float_as_uint(oy0), __float_as_uint(ox1), __float_as_uint(oy1));
+    }
+    return out;
+}
+
+// Position of vector `e` (element index in 16-byte vectors): returns false for a V-head
+// vector, else the float4 index into the table.
+__device__ __forceinline__ bool rope_locate(const SaRopeShape& sh, uint64_t e, uint32_t* tab_idx) {
+    uint64_t row = e / sh.vecs_per_row;
+    uint32_t r = (uint32_t)(e - row * sh.vecs_per_row);
+    if (r >= sh.rotated_vecs) return false;
+    uint32_t tok = (uint32_t)(row % sh.T);
+    uint32_t pos = r % sh.vecs_per_head;
+    *tab_idx = tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec;
+    return true;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kMaxThreads, 1)
+sa_rope_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ x, const float4* __restrict__ table,
+               const __grid_constant__ SaRopeShape sh) {
+    const uint32_t lane = sa_lane();
+    sa_for_each_chunk(s, [&](uint64_t first_vec) {
+        if (first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end && sh.vecs_per_row >= SA_CHUNK_VECS) {
+            // whole chunk: one 64-bit division per chunk, then 32-bit bookkeeping per vector
+            const uint64_t e0 = first_vec - s.lead;
+            const uint64_t row0 = e0 / sh.vecs_per_row;
+            const uint32_t r0 = (uint32_t)(e0 - row0 * sh.vecs_per_row) + lane;
+            const uint32_t tok0 = (uint32_t)(row0 % sh.T);
+            uint4* p = x + e0 + lane;
+            uint4 v[SA_VEC_PER_LANE];
+            uint32_t tab_idx[SA_VEC_PER_LANE];
+            bool live[SA_VEC_PER_LANE];
+#pragma unroll
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                uint32_t r = r0 + k * 32, tok = tok0;
+                if (r >= sh.vecs_per_row) { // a chunk is shorter than a row: at most one wrap
+                    r -= sh.vecs_per_row;
+                    tok = (tok + 1 == sh.T) ? 0 : tok + 1;
+                }
+                live[k] = r < sh.rotated_vecs;
+                uint32_t pos = sh.head_shift >= 0 ? (r & (sh.vecs_per_head - 1)) : (r % sh.vecs_per_head);
+                tab_idx[k] = tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec;
+                if (live[k]) v[k] = ld_stream(p + k * 32);
+            }
+#pragma unroll
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k)
+                if (live[k]) p[k * 32] = rope_vec<BF16>(v[k], table + tab_idx[k]);
+        } else {
+#pragma unroll 1
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                uint64_t a = first_vec + k * 32 + lane;
+                uint32_t ti;
+                if (a >= s.lead && a < s.end && rope_locate(sh, a - s.lead, &ti)) {
+                    uint4* p = x + (a - s.lead);
+                    *p = rope_vec<BF16>(ld_stream(p), table + ti);
+                }
+            }
+        }
+    });
+}
+
+// ---------------------------------------------------------------------------
+// out = bf16(a * sigmoid(a) * b * scale)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t a, uint32_t b, float scale) {
+    float a0 = __uint_as_float(a << 16), a1 = __uint_as_float(a & 0xffff0000u);
+    float b0 = __uint_as_float(b << 16), b1 = __uint_as_float(b & 0xffff0000u);
+    float s0 = __fdividef(1.0f, 1.0f + __expf(-a0)), s1 = __fdividef(1.0f, 1.0f + __expf(-a1));
+    __nv_bfloat162 r = __floats2bfloat162_rn(((a0 * s0) * b0) * scale, ((a1 * s1) * b1) * scale);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__device__ __forceinline__ uint4 silu_mul_vec(uint4 a, uint4 b, float scale) {
+    return make_uint4(silu_mul_pair(a.x, b.x, scale), silu_mul_pair(a.y, b.y, scale),
+                      silu_mul_pair(a.z, b.z, scale), silu_mul_pair(a.w, b.w, scale));
+}
+
+__global__ void __launch_bounds__(kMaxThreads, 1)
+sa_silu_mul_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ out, const uint4* __restrict__ a,
+                   const uint4* __restrict__ b, float scale) {
+    const uint32_t lane = sa_lane();
+    sa_for_each_chunk(s, [&](uint64_t first_vec) {
+        if (first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end) {
+            const uint64_t e = first_vec - s.lead + lane;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) { // two halves of four vectors: 8 loads in flight, 32 data registers
+                uint4 ra[4], rb[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    ra[k] = ld_stream(a + e + (h * 4 + k) * 32);
+                    rb[k] = ld_stream(b + e + (h * 4 + k) * 32);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) out[e + (h * 4 + k) * 32] = silu_mul_vec(ra[k], rb[k], scale);
+            }
+        } else {
+#pragma unroll 1
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                uint64_t v = first_vec + k * 32 + lane;
+                if (v >= s.lead && v < s.end)
+                    out[v - s.lead] = silu_mul_vec(ld_stream(a + (v - s.lead)), ld_stream(b + (v - s.lead)), scale);
+            }
+        }
+    });
+}
+
+} // namespace
+
+cudaError_t sa_launch_memcpy(const SaSched& s, int grid, int threads, void* dst, const void* src, cudaStream_t stream) {
+    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)dst, (const uint4*)src);
+    return cudaGetLastError();
+}
+
+cudaError_t sa_launch_rope(const SaSched& s, int grid, int threads, void* x, const float* table,
+                           const SaRopeShape& sh, bool bf16, cudaStream_t stream) {
+    if (bf16) sa_rope_kernel<true><<<grid, threads, 0, stream>>>(s, (uint4*)x, (const float4*)table, sh);
+    else sa_rope_kernel<false><<<grid, threads, 0, stream>>>(s, (uint4*)x, (const float4*)table, sh);
+    return cudaGetLastError();
+}
+
+cudaError_t sa_launch_silu_mul(const SaSched& s, int grid, int threads, void* out, const void* a, const void* b,
+                               float scale, cudaStream_t stream) {
+    sa_silu_mul_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
+    return cudaGetLastError();
+}

@@ -1,0 +1,23 @@
+// Launch interface of the ahead-of-time kernels (sa_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sa_sched.cuh"
+
+// Geometry of a packed [B, T, Nq + 2 Nkv, HS] tensor in 16-byte vectors.
+struct SaRopeShape {
+    uint32_t vecs_per_head;      // HS * elem_size / 16
+    uint32_t vecs_per_row;       // (Nq + 2 Nkv) * vecs_per_head
+    uint32_t rotated_vecs;       // (Nq + Nkv) * vecs_per_head: Q and K heads come first in a row
+    uint32_t T;
+    uint32_t tab_vecs_per_token; // float4 entries of the cos/sin table per token = HS / 4
+    uint32_t tab_vecs_per_vec;   // float4 table entries consumed per data vector (bf16: 2, fp32: 1)
+    int32_t head_shift;          // log2(vecs_per_head) if it is a power of two, else -1
+};
+
+cudaError_t sa_launch_memcpy(const SaSched& s, int grid, int threads, void* dst, const void* src, cudaStream_t stream);
+cudaError_t sa_launch_rope(const SaSched& s, int grid, int threads, void* x, const float* table,
+                           const SaRopeShape& sh, bool bf16, cudaStream_t stream);
+cudaError_t sa_launch_silu_mul(const SaSched& s, int grid, int threads, void* out, const void* a, const void* b,
+                               float scale, cudaStream_t stream);

@@ -1,0 +1,51 @@
+// Topology discovery for one GPU: which L2 side every SM is nearest to, the
+// XOR hash that flips the side inside a 2 MiB page, and the side of arbitrary
+// addresses (physical pages, 4 KiB chunks) by latency probing.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "sa_sched.cuh"
+
+struct SaTopology {
+    int device = -1;
+    int num_sms = 0;
+    int sms_seen = 0;
+    int max_smid = -1;
+    uint8_t side_index[SA_MAX_SM] = {0}; // byte = side | ordinal << 1 (the reference's format, sideaware.cu:669-675)
+    int count[2] = {0, 0};
+    int min_per_side = 0;
+    uint32_t hash = 0;            // toggling bits among address bits 4..20
+    bool hash_usable = false;     // bit 12 set, nothing below, validated on random offsets
+    int validation_offsets = 0;
+    int validation_errors = 0;
+    double confidence = 0.0;      // min over SMs of |hamming - n/2| / (n/2)
+    uint32_t thr[SA_MAX_SM] = {0}, near_lat[SA_MAX_SM] = {0}, far_lat[SA_MAX_SM] = {0};
+    std::string json;             // raw data for diagnostics
+};
+
+struct SaProbeDevice; // device-side buffers, opaque
+
+// Allocates the probe buffers on `device` (which must be current) and runs discovery
+// on `probe_page_va`, one zero-filled, 2 MiB aligned physical page owned by the caller.
+// Returns cudaSuccess or the failing CUDA error; `why` receives a description.
+cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** out, SaTopology* topo, std::string* why);
+void sa_probe_destroy(SaProbeDevice* p);
+
+// Side (0/1) of each address in `addrs` (device-accessible memory that may hold
+// live data; probing adds zero atomically and changes nothing).  Synchronous.
+cudaError_t sa_probe_sides(SaProbeDevice* p, const SaTopology& topo, const uint64_t* addrs, int n,
+                           uint8_t* sides_out, cudaStream_t stream, int* ambiguous_out);
+
+// Device pointers owned by the probe object.
+unsigned char* sa_probe_gpu_side_index(SaProbeDevice* p);
+uint32_t* sa_probe_ticket_slot(SaProbeDevice* p); // next free ticket slot (round robin)
+
+// Pure host analysis of a latency matrix lat[sm][addr] (exposed for CPU tests).
+// offsets[j] is the byte offset of address j inside the probe page; offsets[0] == 0,
+// offsets[1..17] == 1<<4 .. 1<<20, the rest are validation offsets.
+void sa_analyse_latency_matrix(const std::vector<uint32_t>& lat, int num_rows, const std::vector<int>& row_smid,
+                               const std::vector<uint32_t>& offsets, SaTopology* topo);

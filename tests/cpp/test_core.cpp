@@ -1,0 +1,426 @@
+// CPU tests of the library's host-side logic, built with g++ (no GPU, no CUDA calls):
+//   sched     every 16-byte vector is visited exactly once by the ticket scheduler,
+//             for any side placement, hash, base address and array length
+//   alloc     allocator state machine on a simulated driver with fault injection
+//   topology  SM-side / hash discovery on synthetic latency matrices
+// Usage: test_core <sched|alloc|topology|all>
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <random>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../../l2_torch_alloc_b200/csrc/sa_alloc.hpp"
+#include "../../l2_torch_alloc_b200/csrc/sa_probe.hpp"
+#include "../../l2_torch_alloc_b200/csrc/sa_sched.cuh"
+
+static int g_failures = 0;
+#define CHECK(cond)                                                                  \
+    do {                                                                             \
+        if (!(cond)) {                                                               \
+            std::printf("CHECK failed: %s  (%s:%d)\n", #cond, __FILE__, __LINE__);   \
+            ++g_failures;                                                            \
+        }                                                                            \
+    } while (0)
+
+// ---------------------------------------------------------------------------
+// scheduler: replay what the device loop does (sa_for_each_chunk) for both sides
+// ---------------------------------------------------------------------------
+static void sched_case(uint64_t addr, uint64_t num_vecs, uint32_t hash, uint32_t placement, bool reverse,
+                       uint32_t warps_per_side, uint32_t forced_dc_per_ticket) {
+    SaSched s;
+    std::memset(&s, 0, sizeof(s));
+    s.hash = hash;
+    s.placement = placement;
+    s.reverse = reverse;
+    s.dc_per_ticket = forced_dc_per_ticket;
+    sa_sched_geometry(s, addr, num_vecs, warps_per_side);
+    CHECK(s.lead < SA_DC_VECS);
+    CHECK(s.end == s.lead + num_vecs);
+    CHECK((uint64_t)s.num_tickets * s.dc_per_ticket >= s.num_dc);
+    std::vector<uint8_t> hits(num_vecs, 0);
+    std::vector<uint8_t> by_side(num_vecs, 0);
+    for (uint32_t side = 0; side < 2; ++side)
+        for (uint32_t t = 0; t < s.num_tickets; ++t)
+            for (uint32_t d = 0; d < s.dc_per_ticket; ++d) {
+                sa_u64 first;
+                if (!sa_ticket_chunk(s, t, d, side, &first)) break;
+                if (!(first < s.end && first + SA_CHUNK_VECS > s.lead)) continue;
+                for (uint32_t v = 0; v < SA_CHUNK_VECS; ++v) {
+                    uint64_t a = first + v;
+                    if (a >= s.lead && a < s.end) {
+                        hits[a - s.lead]++;
+                        by_side[a - s.lead] = (uint8_t)side;
+                    }
+                }
+            }
+    bool once = true;
+    for (uint64_t i = 0; i < num_vecs; ++i) once = once && hits[i] == 1;
+    CHECK(once);
+    // in aware mode the worker's side equals the hash-predicted side of the byte address
+    if (placement == SA_PLACE_AWARE && hash) {
+        bool match = true;
+        for (uint64_t i = 0; i < num_vecs; i += 37) {
+            uint32_t predicted = sa_parity32((uint32_t)(addr + i * 16) & hash);
+            match = match && predicted == by_side[i];
+        }
+        CHECK(match);
+    }
+    if (placement == SA_PLACE_WRONG && hash) {
+        bool inverted = true;
+        for (uint64_t i = 0; i < num_vecs; i += 41) {
+            uint32_t predicted = sa_parity32((uint32_t)(addr + i * 16) & hash);
+            inverted = inverted && predicted != by_side[i];
+        }
+        CHECK(inverted);
+    }
+}
+
+static void test_sched() {
+    const uint32_t hashes[] = {0x1EF000u | (1u << 21), 0xB3000u | (1u << 21), 0x1000u | (1u << 21), 0u};
+    std::mt19937_64 rng(1234);
+    // dense small sizes: every vector count up to 3 double chunks, aligned and unaligned bases
+    for (uint64_t n = 1; n <= 3 * SA_DC_VECS + 5; n += (n < 40 ? 1 : 61)) {
+        for (uint64_t off : {0ull, 16ull, 4096ull, 4112ull, 8176ull}) {
+            sched_case(0x7f0000200000ull + off, n, hashes[0], SA_PLACE_AWARE, false, 2368, 0);
+            sched_case(0x7f0000200000ull + off, n, hashes[1], SA_PLACE_UNAWARE, true, 8, 0);
+        }
+    }
+    // shapes the reference's own test copies (test.py:310-326), in 16-byte vectors
+    const uint64_t shapes[] = {4ull * 777 * 4 / 16, 1000ull * 1000 * 2 / 16, 1000ull * 1000 * 8 / 16, 10000ull * 1000 * 4 / 16};
+    for (uint64_t n : shapes)
+        for (uint32_t p : {SA_PLACE_AWARE, SA_PLACE_UNAWARE, SA_PLACE_WRONG})
+            sched_case(0x7f1234600000ull, n, hashes[0], p, false, 2368, 0);
+    // random cases: sizes up to 64 MiB, any 16-byte aligned base, every ticket length
+    for (int i = 0; i < 60; ++i) {
+        uint64_t n = 1 + rng() % (4u << 20);
+        uint64_t addr = 0x7e0000000000ull + (rng() % (1ull << 30)) * 16;
+        uint32_t per = (uint32_t)(rng() % 9); // 0 = automatic
+        sched_case(addr, n, hashes[rng() % 4], (uint32_t)(rng() % 3), rng() & 1, 1 + rng() % 3000, per);
+    }
+    std::printf("sched: done\n");
+}
+
+// ---------------------------------------------------------------------------
+// allocator on a simulated driver
+// ---------------------------------------------------------------------------
+struct FakeDriver : SaBackend {
+    uint64_t next_handle = 1, next_va = 0x7f0000000000ull;
+    size_t capacity_pages = 1 << 20;
+    std::map<uint64_t, int> page_side;       // live handles -> true side
+    std::map<uint64_t, size_t> reservations; // va -> bytes
+    std::map<uint64_t, uint64_t> mappings;   // va -> handle
+    std::set<uint64_t> accessible;
+    std::mt19937 rng{7};
+    int fail_create_after = -1, fail_map_after = -1, fail_reserve_after = -1, fail_access_after = -1, fail_probe_after = -1;
+    int syncs = 0, stream_syncs = 0;
+    int bias_percent = 50; // chance that a new page is on side 1
+
+    static bool tick(int& counter) {
+        if (counter < 0) return false;
+        if (counter == 0) { counter = -1; return true; }
+        --counter;
+        return false;
+    }
+    int create_page(uint64_t* handle, bool) override {
+        if (tick(fail_create_after) || page_side.size() >= capacity_pages) return 2;
+        *handle = next_handle++;
+        page_side[*handle] = (int)(rng() % 100) < bias_percent;
+        return 0;
+    }
+    void release_page(uint64_t handle) override {
+        CHECK(page_side.count(handle) == 1);
+        for (auto& m : mappings) CHECK(m.second != handle);
+        page_side.erase(handle);
+    }
+    int reserve_va(uint64_t* va, size_t bytes) override {
+        if (tick(fail_reserve_after)) return 2;
+        CHECK(bytes % kSaPageBytes == 0);
+        // alternate the bit-21 phase of what the "driver" returns
+        if (rng() & 1) next_va += kSaPageBytes;
+        *va = next_va;
+        next_va += bytes + 4 * kSaPageBytes;
+        reservations[*va] = bytes;
+        return 0;
+    }
+    void free_va(uint64_t va, size_t bytes) override {
+        auto it = reservations.find(va);
+        CHECK(it != reservations.end());
+        if (it != reservations.end()) {
+            CHECK(it->second == bytes); // the range must be freed with the size it was reserved with
+            for (auto& m : mappings) CHECK(!(m.first >= va && m.first < va + bytes));
+            reservations.erase(it);
+        }
+    }
+    bool reserved(uint64_t va) {
+        for (auto& r : reservations)
+            if (va >= r.first && va + kSaPageBytes <= r.first + r.second) return true;
+        return false;
+    }
+    int map_page(uint64_t va, uint64_t handle) override {
+        if (tick(fail_map_after)) return 1;
+        CHECK(reserved(va));
+        CHECK(mappings.count(va) == 0);
+        CHECK(page_side.count(handle) == 1);
+        for (auto& m : mappings) CHECK(m.second != handle);
+        mappings[va] = handle;
+        return 0;
+    }
+    void unmap_page(uint64_t va) override {
+        CHECK(mappings.count(va) == 1);
+        mappings.erase(va);
+        accessible.erase(va);
+    }
+    int set_access(uint64_t va, size_t bytes) override {
+        if (tick(fail_access_after)) return 1;
+        for (uint64_t a = va; a < va + bytes; a += kSaPageBytes) {
+            CHECK(mappings.count(a) == 1);
+            accessible.insert(a);
+        }
+        return 0;
+    }
+    int probe_pages(uint64_t va, int n, uint8_t* sides, void*) override {
+        if (tick(fail_probe_after)) return 1;
+        for (int i = 0; i < n; ++i) {
+            uint64_t a = va + (uint64_t)i * kSaPageBytes;
+            CHECK(accessible.count(a) == 1);
+            sides[i] = (uint8_t)page_side[mappings[a]];
+        }
+        return 0;
+    }
+    void device_sync() override { ++syncs; }
+    void stream_sync(void*) override { ++stream_syncs; }
+
+    // pages of a live block: mapped, accessible, and on the side bit 21 of their address says
+    int wrong_side_pages(uint64_t base, size_t bytes) {
+        int wrong = 0;
+        for (uint64_t a = base; a < base + bytes; a += kSaPageBytes) {
+            CHECK(mappings.count(a) == 1);
+            CHECK(accessible.count(a) == 1);
+            wrong += page_side[mappings[a]] != (int)((a >> 21) & 1);
+        }
+        return wrong;
+    }
+};
+
+static void test_alloc() {
+    SaAllocConfig cfg;
+    {   // basic: alignment, side placement, phase rule, reuse
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t p1 = a.malloc(100u << 20, (void*)1, cfg);
+        CHECK(p1 != 0 && p1 % kSaPageBytes == 0);
+        CHECK(d.wrong_side_pages(p1, 100u << 20) == 0);
+        uint64_t p2 = a.malloc((100u << 20) - 5, (void*)1, cfg); // same page-rounded size => same phase
+        CHECK(p2 != 0 && ((p1 >> 21) & 1) == ((p2 >> 21) & 1));
+        CHECK(a.phase_of_size(100u << 20) == (int)((p1 >> 21) & 1));
+        CHECK(d.wrong_side_pages(p2, 100u << 20) == 0);
+        CHECK(a.owns(p1) && !a.owns(p1 + kSaPageBytes));
+        size_t mapped_before = d.mappings.size();
+        CHECK(a.free(p1, (void*)1));
+        CHECK(!a.free(p1, (void*)1));                 // double free is "not ours"
+        CHECK(d.mappings.size() == mapped_before);     // free never unmaps
+        uint64_t p3 = a.malloc(100u << 20, (void*)1, cfg);
+        CHECK(p3 == p1);                               // exact-size reuse
+        CHECK(d.stream_syncs == 0);
+        a.free(p3, (void*)1);
+        uint64_t p4 = a.malloc(100u << 20, (void*)2, cfg); // other stream => wait for the previous user
+        CHECK(p4 == p1 && d.stream_syncs == 1);
+        SaAllocStats st = a.stats();
+        CHECK(st.reuse_hits == 2 && st.bytes_live == 2 * (100ull << 20) && st.bytes_cached == 0);
+        a.free(p4, (void*)2);
+        a.free(p2, (void*)1);
+        size_t released = a.release_unused();
+        CHECK(released == d.next_handle * 0 + released && d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+        CHECK(released >= 2 * (100ull << 20));
+    }
+    {   // one-page and odd-page blocks
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        for (size_t sz : {1ul, (size_t)kSaPageBytes, 3 * kSaPageBytes, 7 * kSaPageBytes + 1}) {
+            uint64_t p = a.malloc(sz, nullptr, cfg);
+            size_t bytes = (sz + kSaPageBytes - 1) / kSaPageBytes * kSaPageBytes;
+            CHECK(p != 0 && d.wrong_side_pages(p, bytes) == 0);
+        }
+    }
+    {   // fault injection: every k-th driver call of each kind fails once; state must stay consistent
+        for (int kind = 0; kind < 5; ++kind)
+            for (int k = 0; k < 40; k += 3) {
+                FakeDriver d;
+                SaAllocator a(&d, false);
+                uint64_t warm = a.malloc(8u << 20, nullptr, cfg);
+                CHECK(warm != 0);
+                int* knob = kind == 0 ? &d.fail_create_after : kind == 1 ? &d.fail_map_after : kind == 2 ? &d.fail_reserve_after
+                          : kind == 3 ? &d.fail_access_after : &d.fail_probe_after;
+                *knob = k;
+                uint64_t p = a.malloc(64u << 20, nullptr, cfg); // the ladder retries, so this normally still succeeds
+                if (p) CHECK(d.wrong_side_pages(p, 64u << 20) >= 0);
+                // conservation: every live handle is either mapped in a live/cached block or pooled
+                SaAllocStats st = a.stats();
+                size_t accounted = st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes;
+                CHECK(accounted == d.page_side.size());
+                CHECK(d.mappings.size() == (st.bytes_live + st.bytes_cached) / kSaPageBytes);
+                if (p) a.free(p, nullptr);
+                a.free(warm, nullptr);
+                a.release_unused();
+                CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+            }
+    }
+    {   // out of memory: the ladder unmaps the cache, then gives up cleanly
+        FakeDriver d;
+        d.capacity_pages = 64;
+        SaAllocator a(&d, false);
+        uint64_t p = a.malloc(40 * kSaPageBytes, nullptr, cfg);
+        CHECK(p != 0);
+        a.free(p, nullptr);
+        uint64_t q = a.malloc(48 * kSaPageBytes, nullptr, cfg); // needs the cached block's pages back
+        CHECK(q != 0);
+        CHECK(a.stats().bytes_cached == 0);
+        uint64_t r = a.malloc(40 * kSaPageBytes, nullptr, cfg); // cannot fit
+        CHECK(r == 0);
+        CHECK(a.owns(q));
+        CHECK(d.page_side.size() <= 64);
+        a.free(q, nullptr);
+        uint64_t s = a.malloc(60 * kSaPageBytes, nullptr, cfg); // unbalanced pool: cross-side pages allowed, still correct
+        CHECK(s != 0);
+    }
+    {   // threshold trimming: least recently freed blocks go first, down to the end threshold
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        SaAllocConfig c2 = cfg;
+        c2.trim_start = 64u << 20;
+        c2.trim_end = 16u << 20;
+        std::vector<uint64_t> ps;
+        for (int i = 0; i < 10; ++i) ps.push_back(a.malloc((size_t)(8 + 2 * i) << 20, nullptr, c2));
+        for (uint64_t p : ps) a.free(p, nullptr);
+        CHECK(a.stats().bytes_cached == 170ull << 20);
+        uint64_t p = a.malloc(4u << 20, nullptr, c2); // miss -> trim to <= 16 MiB
+        CHECK(p != 0);
+        SaAllocStats st = a.stats();
+        CHECK(st.bytes_cached <= (16u << 20) && st.trims == 1 && d.syncs >= 2);
+        uint64_t again = a.malloc((size_t)(8 + 2 * 9) << 20, nullptr, c2); // most recently freed survived? (26 MiB > 16: no)
+        CHECK(again != 0);
+    }
+    {   // skewed physical side distribution still yields correctly placed blocks
+        FakeDriver d;
+        d.bias_percent = 80;
+        SaAllocator a(&d, false);
+        uint64_t p = a.malloc(256u << 20, nullptr, cfg);
+        CHECK(p != 0 && d.wrong_side_pages(p, 256u << 20) == 0);
+    }
+    {   // compression keeps separate pools and cache keys
+        FakeDriver d;
+        SaAllocator a(&d, true);
+        SaAllocConfig c2 = cfg;
+        uint64_t p = a.malloc(8u << 20, nullptr, c2);
+        a.free(p, nullptr);
+        c2.compression = true;
+        uint64_t q = a.malloc(8u << 20, nullptr, c2);
+        CHECK(q != 0 && q != p);
+    }
+    {   // long random churn: blocks never overlap, pages are conserved
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        std::mt19937 rng(3);
+        std::vector<std::pair<uint64_t, size_t>> live;
+        for (int i = 0; i < 3000; ++i) {
+            if (live.empty() || (rng() % 3)) {
+                size_t sz = (size_t)(1 + rng() % 64) << 20;
+                uint64_t p = a.malloc(sz, (void*)(uintptr_t)(rng() % 3), cfg);
+                CHECK(p != 0);
+                for (auto& l : live) CHECK(!(p < l.first + l.second && l.first < p + sz));
+                live.push_back({p, sz});
+            } else {
+                size_t k = rng() % live.size();
+                CHECK(a.free(live[k].first, nullptr));
+                live.erase(live.begin() + k);
+            }
+        }
+        SaAllocStats st = a.stats();
+        CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.page_side.size());
+    }
+    std::printf("alloc: done\n");
+}
+
+// ---------------------------------------------------------------------------
+// topology analysis on synthetic latencies
+// ---------------------------------------------------------------------------
+static std::vector<uint32_t> offsets64() {
+    std::vector<uint32_t> off{0};
+    for (int b = 4; b <= 20; ++b) off.push_back(1u << b);
+    std::mt19937 rng(99);
+    while (off.size() < 64) {
+        uint32_t o = rng() & 0x1FFFF0u;
+        if (o && (o & (o - 1))) off.push_back(o);
+    }
+    return off;
+}
+
+static void topo_case(uint32_t true_hash, int num_sms, int noise, int far_extra, bool sm0_far_from_addr0, bool expect_usable) {
+    std::vector<uint32_t> off = offsets64();
+    std::mt19937 rng(num_sms * 31 + noise);
+    std::vector<int> sm_side(num_sms);
+    for (int i = 0; i < num_sms; ++i) sm_side[i] = (i == 0) ? 0 : (int)(rng() & 1);
+    std::vector<uint32_t> lat((size_t)num_sms * off.size());
+    std::vector<int> smid(num_sms);
+    for (int i = 0; i < num_sms; ++i) {
+        smid[i] = i;
+        uint32_t base = 5000 + (rng() % 1500); // SMs differ in their distance to L2
+        for (size_t j = 0; j < off.size(); ++j) {
+            int addr_side = (int)sa_parity32(off[j] & true_hash) ^ (sm0_far_from_addr0 ? 1 : 0);
+            bool far = addr_side != sm_side[i];
+            lat[i * off.size() + j] = base + (far ? far_extra : 0) + (noise ? rng() % noise : 0);
+        }
+    }
+    SaTopology t;
+    t.num_sms = num_sms;
+    t.max_smid = num_sms - 1;
+    sa_analyse_latency_matrix(lat, num_sms, smid, off, &t);
+    if (expect_usable) {
+        CHECK(t.hash == true_hash);
+        CHECK(t.hash_usable);
+        CHECK(t.validation_errors == 0);
+        int c[2] = {0, 0};
+        bool sides_ok = true;
+        for (int i = 0; i < num_sms; ++i) {
+            sides_ok = sides_ok && (t.side_index[i] & 1) == sm_side[i];
+            CHECK((t.side_index[i] >> 1) == c[sm_side[i]]); // ordinals count up per side
+            c[sm_side[i]]++;
+        }
+        CHECK(sides_ok);
+        CHECK(t.count[0] == c[0] && t.count[1] == c[1] && t.min_per_side == std::min(c[0], c[1]));
+        CHECK(t.confidence > 0.9);
+        CHECK(!t.json.empty());
+    } else {
+        CHECK(!t.hash_usable);
+    }
+}
+
+static void test_topology() {
+    topo_case(0x1EF000u, 148, 300, 3000, false, true);  // the mask the reference's author saw on a Blackwell part
+    topo_case(0x1EF000u, 148, 300, 3000, true, true);
+    topo_case(0xB3000u, 132, 800, 2500, false, true);   // Hopper-like
+    topo_case(0xAB000u, 132, 100, 1200, true, true);
+    topo_case(0x1000u, 8, 50, 2000, false, true);
+    topo_case(0x1EF000u, 148, 300, 0, false, false);    // no near/far difference at all: must refuse
+    topo_case(0x1EE000u, 148, 300, 3000, false, false); // 8 KiB granularity: chunk pairing would not hold
+    topo_case(0x1EF800u, 148, 300, 3000, false, false); // side flips inside a 4 KiB chunk
+    std::printf("topology: done\n");
+}
+
+int main(int argc, char** argv) {
+    std::string what = argc > 1 ? argv[1] : "all";
+    if (what == "sched" || what == "all") test_sched();
+    if (what == "alloc" || what == "all") test_alloc();
+    if (what == "topology" || what == "all") test_topology();
+    if (g_failures) {
+        std::printf("%d CHECK(s) failed\n", g_failures);
+        return 1;
+    }
+    std::printf("OK\n");
+    return 0;
+}

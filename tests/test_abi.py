@@ -1,0 +1,114 @@
+"""The drop-in boundary, checked without a GPU: the library builds, loads, exports
+every symbol that include/sideaware.h declares (and that the reference exports,
+sideaware.cu:1278-1524), fails loudly instead of falling back when there is no
+device, and compiles functor headers for sm_100a through NVRTC."""
+import os
+import re
+
+import pytest
+
+import l2_torch_alloc_b200 as pkg
+from l2_torch_alloc_b200 import _binding, build, functors
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# the 26 entry points of the reference's extern "C" block
+REFERENCE_SYMBOLS = """
+sideaware_malloc_async sideaware_free_async sideaware_malloc sideaware_free sideaware_release_unused
+sideaware_malloc_auto sideaware_free_auto sideaware_elementwise sideaware_one_to_one sideaware_memcpy
+sideaware_create_kernel_advanced sideaware_create_kernel sideaware_compression sideaware_alloc_threshold
+sideaware_prealloc_config sideaware_free_mapped_thresholds sideaware_write_sass sideaware_fill_side_index
+sideaware_gpu_side_index sideaware_cpu_side_index sideaware_sm_side_summary sideaware_num_sms
+sideaware_num_sm_side0 sideaware_num_sm_side1 sideaware_min_sm_per_side sideaware_hash_mask
+""".split()
+
+
+@pytest.fixture(scope="module")
+def sa():
+    build.build()
+    return pkg.SideAware()
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "sideaware.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sideaware_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_every_reference_symbol():
+    declared = set(header_symbols())
+    assert len(REFERENCE_SYMBOLS) == 26
+    assert set(REFERENCE_SYMBOLS) <= declared
+
+
+def test_library_exports_every_declared_symbol(sa):
+    for name in header_symbols():
+        assert hasattr(sa.lib, name), f"{name} declared in sideaware.h but not exported"
+    assert set(header_symbols()) == set(_binding.SIGNATURES), "ctypes table and header disagree"
+
+
+def test_no_device_is_a_loud_error_not_a_fallback(sa):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    before = sa.error_count()
+    with pytest.raises(RuntimeError, match="no CUDA device|cannot"):
+        sa.summary()
+    assert sa.error_count() > before
+    with pytest.raises(MemoryError):
+        sa.malloc(16 << 20)
+
+
+def test_missing_library_is_a_loud_error(tmp_path):
+    with pytest.raises(FileNotFoundError, match="build it"):
+        pkg.SideAware(str(tmp_path / "sideaware.so"))
+
+
+def test_create_kernel_registry_needs_no_gpu(sa):
+    assert sa.create_kernel(b"") == 0  # id 0 is memcpy (sideaware.cu:1422-1424)
+    a = sa.create_kernel(functors.MEMCPY)
+    b = sa.create_kernel(functors.silu_mul_bf16())
+    assert a >= 1 and b >= 1 and a != b
+    assert sa.create_kernel(functors.MEMCPY) == a  # same text, same id (sideaware.cu:1434-1438)
+
+
+# the functor of the reference's own test (test.py:191-216), restated: mixed element sizes,
+# two outputs, reverse order, all inputs streamed
+MIXED_HEADER = b"""
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+typedef float o0;
+typedef half o1;
+typedef __nv_bfloat16 i0;
+typedef float i1;
+struct unused {};
+typedef unused o2, o3, i2, i3;
+__device__ void elementwise_op(size_t element_idx, int sideband, o0 &out0, o1 &out1, o2 &out2, o3 &out3,
+                               const i0 &in0, const i1 &in1, const i2 &in2, const i3 &in3) {
+    out0 = (o0)((float)in0 + (float)in1);
+    out1 = (o1)((float)in1 * 10.0f);
+}
+constexpr bool reverse_order = true;
+constexpr bool input_evict[4] = {1,1,1,1};
+"""
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_functor_headers_compile_for_sm100a(sa, wide):
+    headers = {
+        "memcpy": functors.MEMCPY,
+        "mixed": MIXED_HEADER,
+        "silu_mul": functors.silu_mul_bf16(),
+        "rope_f32_mha": functors.rope_forward(1024, 32, 32, 128, False),
+        "rope_bf16_gqa": functors.rope_forward(8192, 32, 8, 128, True),
+        "knobs": functors.MEMCPY + "\n#define DISCARD_INPUTS\nconstexpr bool input_discard[4] = {1,0,0,0};\n"
+                 "#define FORCE_WRONG_SIDE true\n#define LAUNCH_BOUNDS __launch_bounds__(512, 1)\n#define UNROLLED 8\n",
+    }
+    for name, h in headers.items():
+        log = sa.compile_check(h, wide)
+        assert log == "", f"{name}: {log[:2000]}"
+
+
+def test_bad_header_reports_the_compiler_log(sa):
+    log = sa.compile_check(b"typedef int o0; this is not CUDA;")
+    assert "error" in log.lower()
