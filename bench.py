@@ -1,0 +1,535 @@
+#!/usr/bin/env python
+"""Benchmark of the side-aware hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (one "step"): a side-aware memcpy of a 1 GiB uint8 buffer of
+seeded random bytes between two blocks obtained from sideaware_malloc_auto (the
+PyTorch pluggable-allocator entry point), launched through the C ABI
+(sideaware_memcpy).  The metric is GB/s counting read + written bytes.  With
+N > 1 every rank runs an independent replica on its own GPU (the path has no
+cross-GPU exchange, so there is no data-path collective); value is the sum of
+the ranks' bytes over the slowest rank's time.
+
+One JSON line is printed by rank 0.  Besides the contract keys it carries the
+same measurement for the RoPE (bf16, Llama-3-8B shape) and functor workloads
+and for the comparison set: the same kernel run side-unaware and on the wrong
+side, cudaMemcpyAsync and torch's copy_.
+
+--impl reference times the CPU stand-in on the host cores: the reference has no
+CPU memcpy of its own (its check is dst == src, test.py:290-294), so libc memcpy
+over all cores is timed for the headline metric, and the reference's own CPU
+RoPE (oracle/_ref, compiled from example_llmc_rope.cu in place) is reported
+beside it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GiB = 1 << 30
+MEMCPY_BYTES = 1 * GiB
+METRIC = "side-aware memcpy & RoPE GB/s per B200 vs 8 TB/s peak and vs side-unaware copy"
+ROPE_SHAPE = dict(B=8, T=8192, Nq=32, Nkv=8, HS=128)  # Llama-3-8B heads, bf16, in place on q and k
+FUNCTOR_ELEMS = 1 << 30
+HBM_FALLBACK_GBS = 6650.0
+SPEC_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum per 1 GiB launch of sa_memcpy_kernel, from the ncu
+# capture summarised under profiles/ (None until a capture exists)
+MEMCPY_DRAM_TRAFFIC_BYTES = None
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# rank plumbing: barrier and max over ranks (gloo on CPU: no GPU data is exchanged)
+# ---------------------------------------------------------------------------
+class Ranks:
+    def __init__(self, gpus: int):
+        self.rank = env_int("RANK", 0)
+        self.local_rank = env_int("LOCAL_RANK", 0)
+        self.world = env_int("WORLD_SIZE", 1)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29533")
+            dist.init_process_group(backend="gloo", rank=self.rank, world_size=self.world)
+            self.dist = dist
+        elif gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+
+    def max(self, value: float) -> float:
+        if not self.dist:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def sum(self, value: float) -> float:
+        if not self.dist:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t[0])
+
+    def close(self):
+        if self.dist:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# clocks during the timed region (NVML, read only)
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting", 0x10: "sync_boost",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self.power = [], set(), None, []
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _once(self):
+        nv = self.nv
+        try:
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            try:
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            except Exception:  # noqa: BLE001
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+            self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+        except Exception:  # noqa: BLE001
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._once()
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+            self._once()
+
+    def report(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "power_w_max": max(self.power) if self.power else None}
+
+
+# ---------------------------------------------------------------------------
+# timing helpers (CUDA events on the launching stream)
+# ---------------------------------------------------------------------------
+def time_launches(torch, fn, steps, warmup, ranks=None, per_launch=False):
+    """Returns (total_ms, [per-launch ms]) for `steps` calls of fn() after `warmup` untimed calls."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if ranks:
+        ranks.barrier()
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)] if per_launch else None
+    start.record(stream)
+    if per_launch:
+        marks[0].record(stream)
+    for i in range(steps):
+        fn()
+        if per_launch:
+            marks[i + 1].record(stream)
+    end.record(stream)
+    torch.cuda.synchronize()
+    if ranks:
+        ranks.barrier()
+    total = start.elapsed_time(end)
+    each = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)] if per_launch else []
+    return total, each
+
+
+def load_cudart(torch):
+    """The CUDA runtime torch already loaded, for cudaMemcpyAsync on raw pointers."""
+    import ctypes
+    import glob
+    cands = glob.glob(os.path.join(os.path.dirname(torch.__file__), "..", "nvidia", "cuda_runtime", "lib", "libcudart.so*"))
+    for c in cands + ["libcudart.so.12", "/usr/local/cuda/lib64/libcudart.so.12"]:
+        try:
+            rt = ctypes.CDLL(c)
+            break
+        except OSError:
+            continue
+    else:
+        raise SystemExit("CUDA runtime library not found")
+    rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+    return rt
+
+
+def gbs(nbytes, ms):
+    return nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+
+
+# ---------------------------------------------------------------------------
+# CPU legs (the only place this file touches oracle/)
+# ---------------------------------------------------------------------------
+def cpu_memcpy_gbs(nbytes, reps, threads):
+    import numpy as np
+    from oracle import oracle
+    src = np.random.default_rng(0xB200 + 2).integers(0, 256, size=nbytes, dtype=np.uint8)
+    dst = np.zeros_like(src)
+    lib = oracle.lib()
+    lib.oracle_memcpy_mt(dst.ctypes.data, src.ctypes.data, nbytes, threads)  # warm, faults pages in
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        lib.oracle_memcpy_mt(dst.ctypes.data, src.ctypes.data, nbytes, threads)
+        times.append(time.perf_counter() - t0)
+    assert dst[:: 4097].tobytes() == src[:: 4097].tobytes()
+    return 2 * nbytes / statistics.median(times) / 1e9, times
+
+
+def cpu_rope_reference():
+    """The reference's own CPU RoPE at its CPU config (B=4 T=1024 NH=12 HS=64 fp32), single thread
+    as written, from oracle/_ref when present, else the C restatement."""
+    import numpy as np
+    from oracle import oracle
+    B, T, NH, HS = 4, 1024, 12, 64
+    x = np.random.default_rng(0xB200 + 1).uniform(-1, 1, size=(B, T, 3 * NH, HS)).astype(np.float32)
+    tab = oracle.freqs_cis(HS, T, 10000.0, 0)
+    out = np.empty_like(x)
+    kind = "port"
+    if oracle.ref_available():
+        try:
+            R = oracle.ref()
+            fn = lambda: R.ref_apply_rotary_emb_forward(oracle._ptr(out, oracle._f32p), oracle._ptr(x, oracle._f32p),  # noqa: E731
+                                                        oracle._ptr(tab, oracle._f32p), B, T, NH, HS)
+            fn()
+            kind = "reference"
+        except Exception:  # noqa: BLE001
+            kind = "port"
+    if kind == "port":
+        L = oracle.lib()
+        fn = lambda: L.oracle_rope_forward_f32(oracle._ptr(out, oracle._f32p), oracle._ptr(x, oracle._f32p),  # noqa: E731
+                                               oracle._ptr(tab, oracle._f32p), B, T, NH, NH, HS)
+        fn()
+    times = []
+    for _ in range(10):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {"kind": kind, "ms": best * 1e3, "gbs": 2 * x.nbytes / best / 1e9, "cores": 1,
+            "config": "fp32 B=4 T=1024 NH=12 HS=64"}
+
+
+def run_reference(args, ranks):
+    if ranks.rank != 0:
+        ranks.close()
+        return 0
+    threads = os.cpu_count() or 1
+    # each step = one 1 GiB copy over all cores; bounded so K steps end within minutes
+    steps = max(1, min(args.steps, 200))
+    warm = max(1, min(args.warmup, 5))
+    value, times = cpu_memcpy_gbs(MEMCPY_BYTES, warm + steps, threads)
+    times = times[warm:]
+    total = sum(times)
+    value = 2 * MEMCPY_BYTES * len(times) / total / 1e9
+    rope = cpu_rope_reference()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": warm, "ms_per_step": total / len(times) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "memcpy 1 GiB uint8 (seeded uniform random bytes)", "bytes": MEMCPY_BYTES,
+                   "where": "host cores"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{len(times)} x 1 GiB libc memcpy over {threads} threads "
+                                   "(the reference ships no CPU memcpy; its check is dst == src)"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "rope_cpu": rope,
+    }
+    print(json.dumps(line), flush=True)
+    ranks.close()
+    return 0
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_ours(args, ranks):
+    import numpy as np
+    import torch
+
+    import l2_torch_alloc_b200 as pkg
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    dev = ranks.local_rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    sa = pkg.SideAware()  # raises if sideaware.so has not been built
+    lib = sa.lib
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    summary = sa.summary_dict()
+
+    def alloc(nbytes):
+        p = lib.sideaware_malloc_auto(nbytes, dev, sp)
+        if not p:
+            raise MemoryError(sa.last_error())
+        return p
+
+    # ---- headline: 1 GiB memcpy ------------------------------------------------
+    gen = torch.Generator(device="cuda").manual_seed(0xB200 + 2 + ranks.rank)
+    seed_t = torch.randint(0, 256, (MEMCPY_BYTES,), dtype=torch.uint8, device="cuda", generator=gen)
+    src, dst = alloc(MEMCPY_BYTES), alloc(MEMCPY_BYTES)
+    lib.sideaware_memcpy(src, seed_t.data_ptr(), MEMCPY_BYTES, dev, sp)
+    torch.cuda.synchronize()
+    launches_before = sa.stats()["kernel_launches"]
+
+    def step():
+        lib.sideaware_memcpy(dst, src, MEMCPY_BYTES, dev, sp)
+
+    sa.set_placement("aware")
+    with ClockSampler(dev) as clocks:
+        total_ms, each = time_launches(torch, step, args.steps, args.warmup, ranks, per_launch=True)
+    launches = sa.stats()["kernel_launches"] - launches_before - args.warmup
+    worst_ms = ranks.max(total_ms)
+    value = ranks.world * args.steps * 2 * MEMCPY_BYTES / (worst_ms * 1e-3) / 1e9
+    # parity spot check of what was just timed
+    back = torch.empty_like(seed_t)
+    lib.sideaware_memcpy(back.data_ptr(), dst, MEMCPY_BYTES, dev, sp)
+    torch.cuda.synchronize()
+    if not torch.equal(back, seed_t):
+        raise SystemExit("bench: the timed copy is not bit-exact")
+    del back
+
+    peak, peak_kind = measured_peak()
+    avg_launch_ms = statistics.mean(each)
+    achieved = gbs(2 * MEMCPY_BYTES, avg_launch_ms)
+    roofline = {"bound": "hbm", "kernel": "sa_memcpy_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_spec_8000": achieved / SPEC_GBS,
+                "traffic": MEMCPY_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": 2 * MEMCPY_BYTES,
+                "best_launch_ms": min(each), "median_launch_ms": statistics.median(each)}
+
+    # ---- end to end through the C ABI with host buffers ---------------------------
+    e2e_steps = max(3, min(args.steps, 10))
+    h_src = torch.empty(MEMCPY_BYTES, dtype=torch.uint8, pin_memory=True)
+    h_dst = torch.empty(MEMCPY_BYTES, dtype=torch.uint8, pin_memory=True)
+    h_src.copy_(seed_t)
+    torch.cuda.synchronize()
+    rt = load_cudart(torch)
+
+    def e2e_step():
+        rt.cudaMemcpyAsync(src, h_src.data_ptr(), MEMCPY_BYTES, 1, sp)
+        lib.sideaware_memcpy(dst, src, MEMCPY_BYTES, dev, sp)
+        rt.cudaMemcpyAsync(h_dst.data_ptr(), dst, MEMCPY_BYTES, 2, sp)
+
+    e2e_ms, _ = time_launches(torch, e2e_step, e2e_steps, 2, ranks)
+    e2e_worst = ranks.max(e2e_ms)
+    e2e_value = ranks.world * e2e_steps * 2 * MEMCPY_BYTES / (e2e_worst * 1e-3) / 1e9
+    if not torch.equal(h_dst[:: 65537], h_src[:: 65537]):
+        raise SystemExit("bench: end-to-end copy mismatch")
+    e2e = {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": MEMCPY_BYTES, "d2h_bytes_per_step": MEMCPY_BYTES,
+           "steps": e2e_steps, "ms_per_step": e2e_worst / e2e_steps}
+    del h_src, h_dst
+
+    extra = {}
+    if ranks.rank == 0:
+        sub_steps = max(5, min(args.steps, 30))
+        # ---- the comparison set for the same 1 GiB copy -------------------------------
+        comp = {}
+        for mode in ("aware", "unaware", "wrong"):
+            sa.set_placement(mode)
+            ms, ea = time_launches(torch, step, sub_steps, 3, None, per_launch=True)
+            comp[f"kernel_{mode}"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
+        sa.set_placement("aware")
+        ms, ea = time_launches(torch, lambda: rt.cudaMemcpyAsync(dst, src, MEMCPY_BYTES, 3, sp), sub_steps, 3, None, per_launch=True)
+        comp["cudaMemcpyAsync_d2d"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
+        t_dst = torch.empty_like(seed_t)
+        ms, ea = time_launches(torch, lambda: t_dst.copy_(seed_t), sub_steps, 3, None, per_launch=True)
+        comp["torch_copy_"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
+        del t_dst
+        extra["memcpy_comparison"] = comp
+
+        # ---- size sweep 4 MiB .. 8 GiB (threshold lowered so 4 MiB blocks are side-aware too) ----
+        sweep = {}
+        lib.sideaware_alloc_threshold(4 << 20)
+        for shift in range(22, 34):
+            n = 1 << shift
+            try:
+                a, b = alloc(n), alloc(n)
+            except MemoryError:
+                break
+            f = lambda: lib.sideaware_memcpy(b, a, n, dev, sp)  # noqa: E731
+            reps = 40 if n <= (256 << 20) else 10
+            ms, ea = time_launches(torch, f, reps, 3, None, per_launch=True)
+            sweep[str(n)] = {"gbs": gbs(2 * n, statistics.median(ea)), "us": statistics.median(ea) * 1e3}
+            lib.sideaware_free_auto(a, n, dev, sp)
+            lib.sideaware_free_auto(b, n, dev, sp)
+        lib.sideaware_alloc_threshold(8 << 20)
+        lib.sideaware_release_unused()
+        extra["memcpy_sweep"] = sweep
+
+    lib.sideaware_free_auto(src, MEMCPY_BYTES, dev, sp)
+    lib.sideaware_free_auto(dst, MEMCPY_BYTES, dev, sp)
+    del seed_t
+    torch.cuda.synchronize()
+
+    # ---- RoPE bf16 at the Llama-3-8B shape (every rank: its batch shard) ---------------------
+    S = ROPE_SHAPE
+    H = S["Nq"] + 2 * S["Nkv"]
+    rope_elems = S["B"] * S["T"] * H * S["HS"]
+    rope_bytes_moved = 2 * S["B"] * S["T"] * (S["Nq"] + S["Nkv"]) * S["HS"] * 2 + S["T"] * S["HS"] * 4
+    gen = torch.Generator(device="cuda").manual_seed(0xB200 + 3 + ranks.rank)
+    x = torch.randn(rope_elems, dtype=torch.float32, device="cuda", generator=gen).to(torch.bfloat16)
+    qkv = alloc(rope_elems * 2)
+    lib.sideaware_memcpy(qkv, x.data_ptr(), rope_elems * 2, dev, sp)
+    half = S["HS"] // 2
+    inv = 1.0 / (500000.0 ** (torch.arange(0, half, dtype=torch.float32) * 2 / S["HS"]))
+    ang = torch.arange(S["T"], dtype=torch.float32)[:, None] * inv[None, :]
+    table = torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous().cuda()
+
+    def rope_step():
+        rc = lib.sideaware_rope_forward(qkv, table.data_ptr(), S["B"], S["T"], S["Nq"], S["Nkv"], S["HS"], 1, dev, sp)
+        if rc:
+            raise SystemExit(f"rope launch failed: {sa.last_error()}")
+
+    rope_steps = max(5, min(args.steps, 50))
+    rope = {}
+    for mode in (("aware", "unaware", "wrong") if ranks.rank == 0 else ("aware",)):
+        sa.set_placement(mode)
+        ms, ea = time_launches(torch, rope_step, rope_steps, 3, ranks if mode == "aware" else None, per_launch=True)
+        if mode == "aware":
+            worst = ranks.max(ms)
+            rope["aggregate_gbs"] = ranks.world * rope_steps * rope_bytes_moved / (worst * 1e-3) / 1e9
+        rope[mode] = {"gbs": gbs(rope_bytes_moved, statistics.mean(ea)), "best_gbs": gbs(rope_bytes_moved, min(ea)),
+                      "ms": statistics.mean(ea)}
+    sa.set_placement("aware")
+    rope["algorithmic_bytes"] = rope_bytes_moved
+    rope["frac_of_peak"] = rope["aware"]["gbs"] / peak
+    rope["config"] = "bf16 B=8 T=8192 32q+8kv HS=128 theta=500000 in place"
+    lib.sideaware_free_auto(qkv, rope_elems * 2, dev, sp)
+    del x, table
+
+    # ---- functor: out = bf16(a * sigmoid(a) * b * 0.5), 2^30 elements (rank 0) ----------------
+    functor = None
+    if ranks.rank == 0:
+        from l2_torch_alloc_b200 import functors
+        n = FUNCTOR_ELEMS
+        a, b, o = alloc(2 * n), alloc(2 * n), alloc(2 * n)
+        g2 = torch.Generator(device="cuda").manual_seed(0xB200 + 4)
+        chunk = 1 << 27
+        for off in range(0, n, chunk):
+            for buf in (a, b):
+                t = torch.randn(chunk, dtype=torch.float32, device="cuda", generator=g2).to(torch.bfloat16)
+                lib.sideaware_memcpy(buf + 2 * off, t.data_ptr(), 2 * chunk, dev, sp)
+        torch.cuda.synchronize()
+        kid = sa.create_kernel(functors.silu_mul_bf16())
+        scale_bits = int(np.float32(0.5).view(np.int32))
+        f_jit = lambda: lib.sideaware_elementwise(kid, 2 * n, o, None, None, None, a, b, None, None, None, scale_bits, 0, 0, dev, sp)  # noqa: E731
+        f_aot = lambda: lib.sideaware_silu_mul_bf16(o, a, b, 0.5, n, dev, sp)  # noqa: E731
+        functor = {"algorithmic_bytes": 6 * n, "config": "bf16 2^30 elements, three side-tagged buffers"}
+        for name, f in (("aot", f_aot), ("nvrtc", f_jit)):
+            for mode in ("aware", "unaware"):
+                sa.set_placement(mode)
+                ms, ea = time_launches(torch, f, 10, 2, None, per_launch=True)
+                functor[f"{name}_{mode}"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea)}
+        sa.set_placement("aware")
+        functor["frac_of_peak"] = functor["aot_aware"]["gbs"] / peak
+        for buf in (a, b, o):
+            lib.sideaware_free_auto(buf, 2 * n, dev, sp)
+        if sa.error_count():
+            functor["errors"] = sa.last_error()
+
+    line = None
+    if ranks.rank == 0:
+        cpu = None
+        if ranks.world == 1:
+            threads = os.cpu_count() or 1
+            v, times = cpu_memcpy_gbs(MEMCPY_BYTES, 12, threads)
+            cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                   "sample": f"12 x 1 GiB libc memcpy over {threads} threads (the reference has no CPU memcpy)",
+                   "rope": cpu_rope_reference()}
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": ranks.world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": worst_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "memcpy 1 GiB uint8 (seeded uniform random bytes) via sideaware_malloc_auto + sideaware_memcpy",
+                       "bytes": MEMCPY_BYTES, "l2": "inputs larger than L2 (2 GiB touched per step vs 126 MB)",
+                       "parallelism": f"{ranks.world} independent replicas, no collective"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * ranks.world,
+            "clocks": clocks.report(), "topology": summary, "rope": rope, "functor": functor, **extra,
+        }
+        print(json.dumps(line), flush=True)
+    ranks.close()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    ranks = Ranks(args.gpus)
+    if args.impl == "reference":
+        return run_reference(args, ranks)
+    return run_ours(args, ranks)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

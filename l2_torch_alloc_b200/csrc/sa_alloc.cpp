@@ -181,6 +181,7 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
     std::lock_guard<std::mutex> lock(mu_);
     const size_t bytes = round_to_pages(size);
     const bool compressed = cfg.compression && comp_ok_;
+    if (capacity_ && bytes > capacity_) return 0; // can never fit: do not drain the device trying
 
     // 1) exact-size reuse of a block that is still mapped (sideaware.cu:1199-1219)
     auto hit = cache_.find(cache_key(bytes, compressed));
@@ -222,6 +223,12 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
             return base;
         }
     }
+    // nothing worked: do not sit on the pages gathered while trying
+    for (int c = 0; c < 2; ++c)
+        for (int s = 0; s < 2; ++s) {
+            for (auto& pg : pool_[c][s]) be_->release_page(pg.handle);
+            pool_[c][s].clear();
+        }
     return 0;
 }
 

@@ -58,7 +58,9 @@ struct SaAllocStats {
 
 class SaAllocator {
 public:
-    SaAllocator(SaBackend* backend, bool compression_supported) : be_(backend), comp_ok_(compression_supported) {}
+    // capacity_bytes: total device memory (0 = unknown); larger requests fail at once
+    SaAllocator(SaBackend* backend, bool compression_supported, size_t capacity_bytes = 0)
+        : be_(backend), comp_ok_(compression_supported), capacity_(capacity_bytes) {}
     ~SaAllocator();
 
     // Returns the block address or 0.  `cfg` is read at every call (the setters are global).
@@ -95,6 +97,7 @@ private:
 
     SaBackend* be_;
     bool comp_ok_;
+    size_t capacity_ = 0;
     std::mutex mu_;
     std::vector<Page> pool_[2][2]; // [compressed][side]
     std::unordered_map<uint64_t, Block> live_;

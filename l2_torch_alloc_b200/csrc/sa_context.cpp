@@ -184,7 +184,9 @@ bool init_device(SaDevice* dev) {
     dev->summary[4] = (int)(dev->topo.hash | (1u << kSaSideBit));
 
     dev->backend.reset(new CudaBackend(dev));
-    dev->alloc.reset(new SaAllocator(dev->backend.get(), dev->compression_supported));
+    size_t free_bytes = 0, total_bytes = 0;
+    cudaMemGetInfo(&free_bytes, &total_bytes);
+    dev->alloc.reset(new SaAllocator(dev->backend.get(), dev->compression_supported, total_bytes));
     dev->jit = sa_jit_new_device_cache();
     if (const char* dump = std::getenv("SIDEAWARE_DUMP_TOPOLOGY")) {
         std::string path = std::string(dump) + "." + std::to_string(dev->id) + ".json";

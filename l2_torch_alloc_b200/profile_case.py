@@ -1,0 +1,72 @@
+"""Small, self-terminating workloads for profiler captures.
+
+    python -m l2_torch_alloc_b200.profile_case memcpy   [--mib 256] [--reps 4] [--placement aware]
+    python -m l2_torch_alloc_b200.profile_case rope     [--batch 2]  [--reps 4]
+    python -m l2_torch_alloc_b200.profile_case functor  [--mib 256] [--reps 4]
+
+Each case touches more than the 126 MB L2 but well under 2 GB of device memory and
+launches the kernel of interest a handful of times, so a multi-pass capture ends by itself.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+import l2_torch_alloc_b200 as pkg
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["memcpy", "rope", "functor"])
+    ap.add_argument("--mib", type=int, default=256)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--reps", type=int, default=4)
+    ap.add_argument("--placement", default="aware", choices=["aware", "unaware", "wrong"])
+    ap.add_argument("--engine", type=int, default=0)
+    args = ap.parse_args()
+    sa = pkg.SideAware()
+    sa.set_placement(args.placement)
+    sa.lib.sideaware_set_memcpy_engine(args.engine)
+    torch.cuda.set_device(0)
+    if args.case == "memcpy":
+        n = args.mib << 20
+        seed = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
+        a, b = sa.malloc(n), sa.malloc(n)
+        sa.memcpy_ptr(a, seed.data_ptr(), n)
+        for _ in range(args.reps):
+            sa.memcpy_ptr(b, a, n)
+        out = torch.empty_like(seed)
+        sa.memcpy_ptr(out.data_ptr(), b, n)
+        torch.cuda.synchronize()
+        assert torch.equal(out, seed)
+    elif args.case == "rope":
+        B, T, Nq, Nkv, HS = args.batch, 8192, 32, 8, 128
+        n = B * T * (Nq + 2 * Nkv) * HS
+        x = torch.randn(n, device="cuda").to(torch.bfloat16)
+        half = HS // 2
+        inv = 1.0 / (500000.0 ** (torch.arange(0, half, dtype=torch.float32) * 2 / HS))
+        ang = torch.arange(T, dtype=torch.float32)[:, None] * inv[None, :]
+        table = torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous().cuda()
+        q = sa.malloc(2 * n)
+        sa.memcpy_ptr(q, x.data_ptr(), 2 * n)
+        for _ in range(args.reps):
+            sa.rope_forward_ptr(q, table.data_ptr(), B, T, Nq, Nkv, HS, True)
+        torch.cuda.synchronize()
+    else:
+        n = (args.mib << 20) // 2
+        a = sa.malloc(2 * n)
+        b = sa.malloc(2 * n)
+        o = sa.malloc(2 * n)
+        x = torch.randn(n, device="cuda").to(torch.bfloat16)
+        sa.memcpy_ptr(a, x.data_ptr(), 2 * n)
+        sa.memcpy_ptr(b, x.data_ptr(), 2 * n)
+        for _ in range(args.reps):
+            sa.silu_mul_ptr(o, a, b, 0.5, n)
+        torch.cuda.synchronize()
+    assert sa.error_count() == 0, sa.last_error()
+    print("profile case done:", args.case, sa.summary_dict())
+
+
+if __name__ == "__main__":
+    main()

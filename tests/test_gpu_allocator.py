@@ -1,0 +1,150 @@
+"""Allocator and topology behaviour on a B200, through the C ABI.  The reference has
+no tests for these parts; the properties checked are the ones its design promises
+(sideaware.cu:1036-1047: 2 MiB granularity, VA bit 21 == page side, same size ==
+same phase) plus self-consistency of the discovery and of the per-chunk side map."""
+import ctypes
+import json
+import threading
+
+import numpy as np
+import pytest
+
+from tests import cuda_helpers as ch
+
+pytestmark = pytest.mark.gpu
+
+MiB = 1 << 20
+
+
+@pytest.fixture(scope="module")
+def sa():
+    import torch
+    assert torch.cuda.is_available()
+    import l2_torch_alloc_b200 as pkg
+    return pkg.SideAware()
+
+
+def test_topology_is_self_consistent(sa):
+    n, s0, s1, m, h = sa.summary()
+    assert n == sa.lib.sideaware_num_sms() and n >= 100
+    assert s0 + s1 == n and m == min(s0, s1) and m > 0
+    assert s0 == sa.lib.sideaware_num_sm_side0() and s1 == sa.lib.sideaware_num_sm_side1()
+    assert h == sa.lib.sideaware_hash_mask() and (h >> 21) & 1
+    idx = sa.cpu_side_index()
+    assert len(idx) == n and idx[0] & 1 == 0, "the lowest SM id defines side 0"
+    per_side = [[b >> 1 for b in idx if b & 1 == s] for s in (0, 1)]
+    for s in (0, 1):
+        assert per_side[s] == list(range(len(per_side[s]))), "ordinals count up within a side"
+    assert sa.side_index_tensor().cpu().numpy().tobytes() == idx
+    topo = json.loads(sa.topology_json())
+    assert topo["sms_seen"] == n
+    st = sa.stats()
+    print("topology:", sa.summary_dict(), "confidence", st["probe_confidence_ppm"] / 1e6,
+          "validation errors", st["hash_validation_errors"], "usable", topo["hash_usable"])
+    assert topo["hash_usable"], f"no usable side hash on this device: {topo['hash']:#x}"
+    assert (h & 0x1000) and not (h & 0xFFF), "4 KiB chunks must alternate sides"
+    assert st["hash_validation_errors"] == 0 and st["probe_confidence_ppm"] > 700000
+
+
+def test_block_geometry_and_phase_rule(sa):
+    p1 = sa.malloc(64 * MiB)
+    p2 = sa.malloc(64 * MiB - 3)
+    p3 = sa.malloc(66 * MiB)
+    for p in (p1, p2, p3):
+        assert p % (2 * MiB) == 0
+    assert (p1 >> 21) & 1 == (p2 >> 21) & 1, "same page-rounded size, same bit-21 phase"
+    st = sa.stats()
+    assert st["bytes_mapped_live"] >= (64 + 64 + 66) * MiB
+    sa.free(p1)
+    assert sa.malloc(64 * MiB) == p1, "exact-size reuse of the still-mapped block"
+    for p in (p1, p2, p3):
+        sa.free(p)
+    assert sa.stats()["reuse_hits"] >= 1
+
+
+def test_predicted_chunk_sides_match_measurement(sa):
+    """The model (hash over address bits 12..20 plus VA bit 21) against fresh latency probes."""
+    nbytes = 256 * MiB
+    p = sa.malloc(nbytes)
+    pattern = np.random.default_rng(1).integers(0, 256, size=8 * MiB, dtype=np.uint8)
+    ch.h2d(p, pattern)
+    sides = np.frombuffer(sa.chunk_sides(p, nbytes), dtype=np.uint8)
+    assert sides.size == nbytes // 4096
+    pairs = sides.reshape(-1, 2)
+    assert (pairs[:, 0] != pairs[:, 1]).all(), "the halves of every 8 KiB double chunk are on opposite sides"
+    assert abs(int(sides.sum()) - sides.size // 2) == 0
+    mism = sa.verify_chunk_sides(p, nbytes, 2048, 7)
+    print("chunk-side mismatches:", mism, "of 2048; cross-side pages:", sa.stats()["cross_side_pages"])
+    assert 0 <= mism <= 20, f"{mism} of 2048 probed chunks are not on the predicted side"
+    assert np.array_equal(ch.d2h(p, 8 * MiB), pattern), "probing must not modify memory"
+    sa.free(p)
+
+
+def test_release_unused_returns_memory(sa):
+    import torch
+    p = sa.malloc(512 * MiB)
+    sa.free(p)
+    free_before, _ = torch.cuda.mem_get_info()
+    released = int(sa.lib.sideaware_release_unused())
+    free_after, _ = torch.cuda.mem_get_info()
+    assert released >= 512 * MiB
+    assert free_after - free_before >= 500 * MiB
+    st = sa.stats()
+    assert st["bytes_mapped_cached"] == 0 and st["pages_pool_side0"] == 0 and st["pages_pool_side1"] == 0
+
+
+def test_auto_entry_points(sa):
+    lib = sa.lib
+    small = lib.sideaware_malloc_auto(4096, 0, None)      # below the 8 MiB threshold: runtime pool
+    large = lib.sideaware_malloc_auto(32 * MiB, 0, None)  # side-aware
+    assert small and large and large % (2 * MiB) == 0
+    before = sa.stats()
+    lib.sideaware_free_auto(small, 4096, 0, None)
+    lib.sideaware_free_auto(large, 32 * MiB, 0, None)
+    lib.sideaware_free_auto(None, 0, 0, None)
+    after = sa.stats()
+    assert after["bytes_mapped_cached"] == before["bytes_mapped_cached"] + 32 * MiB
+    assert before["small_allocs"] >= 1
+    lib.sideaware_alloc_threshold(2 * MiB)
+    p = lib.sideaware_malloc_auto(3 * MiB, 0, None)
+    assert p % (2 * MiB) == 0 and sa.stats()["bytes_mapped_live"] >= 4 * MiB
+    lib.sideaware_free_auto(p, 3 * MiB, 0, None)
+    lib.sideaware_alloc_threshold(8 * MiB)
+    ch.sync()
+
+
+def test_sync_entry_points_and_status_codes(sa):
+    p = ctypes.c_void_p()
+    assert sa.lib.sideaware_malloc(ctypes.byref(p), 10 * MiB) == 0 and p.value
+    assert sa.lib.sideaware_free(p) == 0
+    huge = ctypes.c_void_p()
+    rc = sa.lib.sideaware_malloc_async(ctypes.byref(huge), 400 << 30, None)  # more than the device holds
+    assert rc == 2 and not huge.value, "out of memory is cudaErrorMemoryAllocation, not a crash"
+    q = sa.malloc(10 * MiB)  # the allocator keeps working afterwards
+    sa.free(q)
+
+
+def test_concurrent_malloc_free(sa):
+    errors = []
+
+    def worker(seed):
+        try:
+            rng = np.random.default_rng(seed)
+            held = []
+            for _ in range(60):
+                if held and rng.random() < 0.5:
+                    sa.free(held.pop(int(rng.integers(len(held)))))
+                else:
+                    held.append(sa.malloc(int(rng.integers(1, 24)) * 2 * MiB))
+            for p in held:
+                sa.free(p)
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(6)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert sa.stats()["bytes_mapped_live"] == 0

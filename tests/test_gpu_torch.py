@@ -1,0 +1,48 @@
+"""torch integration on a B200: CUDAPluggableAllocator entry points and torch.ops.sideaware.*
+(the usage of test.py:14-15, :147-184), each in a fresh process."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_script(args, timeout=900):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, *args], capture_output=True, text=True, timeout=timeout, cwd=ROOT, env=env)
+    return r
+
+
+def test_pluggable_allocator_flow():
+    r = run_script([os.path.join(ROOT, "tests", "pluggable_allocator_script.py"), "400"])
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert lines, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(lines[-1][7:])
+    print(json.dumps(res, indent=1)[:3000])
+    assert r.returncode == 0 and res["ok"], res
+    assert res["stats_mid"]["large_allocs"] >= 1 and res["stats_mid"]["small_allocs"] >= 1
+    assert res["stats_end"]["cross_side_pages"] == 0
+
+
+def test_custom_op_under_torch_compile():
+    code = """
+import torch, l2_torch_alloc_b200 as pkg
+sa = pkg.sideaware_init()
+@torch.compile(fullgraph=True)
+def f(dst, src):
+    torch.ops.sideaware.memcpy(dst, src)
+    return dst
+src = torch.ones((8, 8), device="cuda") * 2.0
+dst = torch.zeros((8, 8), device="cuda")
+out = f(dst, src)
+torch.cuda.synchronize()
+assert torch.equal(out, src) and torch.equal(dst, src)
+print("COMPILED-OK")
+"""
+    r = run_script(["-c", code])
+    assert "COMPILED-OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
