@@ -11,7 +11,7 @@ from typing import Optional
 
 from . import _binding
 
-_state = {"sa": None, "ops_registered": False}
+_state = {"sa": None}
 
 
 def _stream_ptr(stream) -> int:
@@ -207,46 +207,8 @@ class SideAware:
 
     def register_ops(self) -> None:
         """torch.ops.sideaware.{memcpy, one_to_one, elementwise, rope_forward, silu_mul}"""
-        if _state["ops_registered"]:
-            return
-        import torch
-        from torch import Tensor
-
-        sa = self
-
-        def memcpy(dst: Tensor, src: Tensor) -> None:
-            sa.memcpy(dst, src)
-
-        def one_to_one(kernel_id: int, dst: Tensor, src: Tensor) -> None:
-            sa.one_to_one(kernel_id, dst, src)
-
-        def elementwise(kernel_id: int, out0: Tensor, out1: Optional[Tensor], out2: Optional[Tensor],
-                        out3: Optional[Tensor], in0: Optional[Tensor], in1: Optional[Tensor], in2: Optional[Tensor],
-                        in3: Optional[Tensor], sideband_tensor: Optional[Tensor] = None, sideband_value: int = 0,
-                        parallel_chunks: int = 0, forced_sm_per_side: int = 0) -> None:
-            sa.elementwise(kernel_id, out0, out1, out2, out3, in0, in1, in2, in3, sideband_tensor, sideband_value,
-                           parallel_chunks, forced_sm_per_side)
-
-        def rope_forward(qkv: Tensor, freqs_cis: Tensor, n_q_heads: int, n_kv_heads: int) -> None:
-            sa.rope_forward(qkv, freqs_cis, n_q_heads, n_kv_heads)
-
-        def silu_mul(out: Tensor, a: Tensor, b: Tensor, scale: float) -> None:
-            sa.silu_mul(out, a, b, scale)
-
-        lib = torch.library.Library("sideaware", "FRAGMENT")
-
-        def reg(name, fn, mutates):
-            schema = torch.library.infer_schema(fn, mutates_args=mutates)
-            lib.define(name + schema)
-            lib.impl(name, fn, "CUDA")
-
-        reg("memcpy", memcpy, ["dst"])
-        reg("one_to_one", one_to_one, ["dst"])
-        reg("elementwise", elementwise, ["out0", "out1", "out2", "out3", "sideband_tensor"])
-        reg("rope_forward", rope_forward, ["qkv"])
-        reg("silu_mul", silu_mul, ["out"])
-        self._torch_lib = lib
-        _state["ops_registered"] = True
+        from . import torch_ops
+        torch_ops.register(self)
 
 
 # ---------------------------------------------------------------------------
