@@ -44,8 +44,8 @@ FUNCTOR_ELEMS = 1 << 30
 HBM_FALLBACK_GBS = 6650.0
 SPEC_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per 1 GiB launch of sa_memcpy_kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists)
-MEMCPY_DRAM_TRAFFIC_BYTES = None
+# capture summarised in profiles/sa_memcpy_kernel_1GiB_fabric_by_placement.md
+MEMCPY_DRAM_TRAFFIC_BYTES = 2088437504
 
 
 def env_int(name, default):
