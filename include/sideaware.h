@@ -165,6 +165,35 @@ void sideaware_get_stats(sideaware_stats_t* out);
  * owned by the library; for diagnostics. */
 const char* sideaware_topology_json(void);
 
+/* Copy for callers that cannot allocate device memory.  (No counterpart in the
+ * reference.)  Some users of a GPU library run where a cudaMalloc is not an
+ * option: a server that handed all of HBM to its own pool at start-up, so any
+ * further allocation fails; code that runs inside another allocator's callback
+ * and must not re-enter allocation; a shutdown or error path that copies state
+ * out after an out-of-memory condition.  sideaware_memcpy cannot serve them on a
+ * device it has not seen yet, because its first use of a device allocates probe
+ * and bookkeeping buffers.  This entry point never calls cudaMalloc, cudaFree or
+ * any allocating routine: the three work counters the copy kernel needs sit in a
+ * fixed 512-byte array inside the loaded module (each GPU that loads the library
+ * holds those 512 bytes until the process ends).
+ *   - num_bytes: multiple of 16, at most SIDEAWARE_NOALLOC_MAX_BYTES (the work
+ *     counters are 32 bits wide; the cap keeps them far from wrapping); larger
+ *     requests are refused with cudaErrorInvalidValue (1) and a message in
+ *     sideaware_last_error().  out/in: 16-byte aligned device pointers.
+ *   - The first call on a device looks up the array's device address (a lookup,
+ *     not an allocation) with that device made current; make that first call
+ *     before starting any stream capture.
+ *   - The array is shared by every call and keeps the last call's contents, so
+ *     each call first zeroes it on `stream`.  Two calls whose kernels overlap on
+ *     the GPU (different streams, or different threads) race on it and may skip
+ *     or repeat data: issue these copies on one stream, or order them yourself.
+ *   - Side placement is used only if an earlier, allocating call has already
+ *     set the device up; otherwise the copy is side-unaware (same result,
+ *     slower).  The result is bit-identical to sideaware_memcpy either way. */
+#define SIDEAWARE_NOALLOC_MAX_BYTES (1ull << 36) /* 64 GiB per call */
+sideaware_status_t sideaware_memcpy_noalloc(void* out, const void* in, size_t num_bytes, int device,
+                                            sideaware_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -412,3 +412,53 @@ SA_API const char* sideaware_topology_json(void) {
     SaDevice* dev = sa_device(-1);
     return dev ? dev->topo.json.c_str() : "{}";
 }
+
+// ---------------------------------------------------------------------------
+// memcpy without any device-memory allocation
+// ---------------------------------------------------------------------------
+SA_API sideaware_status_t sideaware_memcpy_noalloc(void* out, const void* in, size_t num_bytes, int device,
+                                                   sideaware_stream_t stream) {
+    if (num_bytes == 0) return cudaSuccess;
+    if (!out || !in) {
+        sa_set_error("sideaware_memcpy_noalloc: null pointer");
+        return cudaErrorInvalidValue;
+    }
+    if (num_bytes > SIDEAWARE_NOALLOC_MAX_BYTES) {
+        sa_set_error("sideaware_memcpy_noalloc: %zu bytes is more than this entry point accepts (%llu); split the copy",
+                     num_bytes, (unsigned long long)SIDEAWARE_NOALLOC_MAX_BYTES);
+        return cudaErrorInvalidValue;
+    }
+    const void* ptrs[2] = {out, in};
+    if (!check_launch_args("sideaware_memcpy_noalloc", num_bytes, ptrs, 2)) return cudaErrorInvalidValue;
+    if (device < 0 && cudaGetDevice(&device) != cudaSuccess) {
+        sa_set_error("sideaware_memcpy_noalloc: no CUDA device");
+        return cudaErrorNoDevice;
+    }
+    SaScopedDevice guard(device);
+    int num_sms = 0;
+    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || num_sms <= 0) {
+        sa_set_error("sideaware_memcpy_noalloc: cannot query device %d", device);
+        return cudaErrorInvalidDevice;
+    }
+    // The SM side table exists only if some earlier call set this device up (that set-up
+    // allocates, so it is not done here).  Without it the copy runs side-unaware.
+    SaDevice* dev = sa_device_if_ready(device);
+    SaSched s;
+    std::memset(&s, 0, sizeof(s));
+    const int warps = 32;
+    sa_sched_geometry(s, (uint64_t)in, num_bytes / 16, (uint32_t)(num_sms * warps / 2));
+    int grid = num_sms;
+    int need_blocks = (int)((2ull * s.num_tickets + warps - 1) / warps);
+    if (need_blocks < 1) need_blocks = 1;
+    if (need_blocks < grid) grid = need_blocks;
+    s.total_warps = (uint32_t)(grid * warps);
+    s.placement = SA_PLACE_UNAWARE;
+    if (dev && dev->full_hash) {
+        s.hash = dev->full_hash;
+        s.placement = (uint32_t)sa_config().placement.load();
+        std::memcpy(s.side_of_sm, dev->topo.side_index, SA_MAX_SM);
+    }
+    cudaError_t e = sa_launch_memcpy_noalloc(s, device, grid, warps * 32, out, in, (cudaStream_t)stream);
+    if (e != cudaSuccess) sa_set_error("sideaware_memcpy_noalloc: %s", cudaGetErrorString(e));
+    return e;
+}

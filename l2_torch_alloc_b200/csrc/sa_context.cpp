@@ -271,3 +271,10 @@ void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, in
     *threads = warps * 32;
     dev->launches.fetch_add(1);
 }
+
+SaDevice* sa_device_if_ready(int device) {
+    std::lock_guard<std::mutex> lock(g_devices_mu);
+    if (device < 0 || device >= (int)g_devices.size() || !g_devices[device]) return nullptr;
+    SaDevice* dev = g_devices[device].get();
+    return dev->ready ? dev : nullptr;
+}

@@ -71,3 +71,7 @@ unsigned long long sa_error_total();
 // whose side-tracking array starts at `track_addr`, and picks grid and block size.
 void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
                        int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads);
+
+// The device's state if some earlier call has already set it up, else nullptr.  Never
+// initialises anything (so it never allocates).
+SaDevice* sa_device_if_ready(int device);

@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "sa_kernels.hpp"
 
 namespace {
@@ -208,5 +210,47 @@ cudaError_t sa_launch_rope(const SaSched& s, int grid, int threads, void* x, con
 cudaError_t sa_launch_silu_mul(const SaSched& s, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream) {
     sa_silu_mul_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// memcpy for callers that must not allocate device memory
+// ---------------------------------------------------------------------------
+// The memcpy kernel needs three ticket counters in global memory.  Normally they come
+// from a buffer the library allocated when the device was first used.  Here they live in
+// a fixed 512-byte array that is part of the loaded module, so no allocation call is made;
+// every GPU that loads the library carries these 512 bytes until the process exits.
+#define SA_NOALLOC_SCRATCH_WORDS 128
+static __device__ __align__(256) unsigned int sa_noalloc_scratch[SA_NOALLOC_SCRATCH_WORDS];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned int* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+} // namespace
+
+// `device` must be the current device.  The first call on a device looks up the device
+// address of the array (in host code the array's name is only a handle, not an address a
+// kernel could use) and keeps it.  Every call then zeroes the counters on `stream` before
+// the kernel runs, because the array is shared by all calls and keeps whatever the last
+// one left behind.
+cudaError_t sa_launch_memcpy_noalloc(SaSched s, int device, int grid, int threads, void* dst, const void* src,
+                                     cudaStream_t stream) {
+    if (device < 0 || device >= kNoAllocMaxDevices) return cudaErrorInvalidDevice;
+    unsigned int* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (!g_noalloc_ptr[device]) {
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, sa_noalloc_scratch);
+            if (e != cudaSuccess) return e;
+            g_noalloc_ptr[device] = (unsigned int*)p;
+        }
+        scratch = g_noalloc_ptr[device];
+    }
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(unsigned int) * SA_NOALLOC_SCRATCH_WORDS, stream);
+    if (e != cudaSuccess) return e;
+    s.tickets = scratch;
+    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)dst, (const uint4*)src);
     return cudaGetLastError();
 }

@@ -21,3 +21,6 @@ cudaError_t sa_launch_rope(const SaSched& s, int grid, int threads, void* x, con
                            const SaRopeShape& sh, bool bf16, cudaStream_t stream);
 cudaError_t sa_launch_silu_mul(const SaSched& s, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream);
+// Same kernel as sa_launch_memcpy with its ticket counters in a static device array (no allocation).
+cudaError_t sa_launch_memcpy_noalloc(SaSched s, int device, int grid, int threads, void* dst, const void* src,
+                                     cudaStream_t stream);
