@@ -522,10 +522,22 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--check-ranks", action="store_true",
+                    help="exercise only the rank plumbing (barrier, max/sum over ranks, rank 0 prints); needs no GPU")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     ranks = Ranks(args.gpus)
+    if args.check_ranks:
+        # every rank pretends to have moved (rank + 1) GB in (rank + 1) ms; the job value uses the slowest rank
+        ranks.barrier()
+        worst = ranks.max(float(ranks.rank + 1))
+        total = ranks.sum(float(ranks.rank + 1))
+        if ranks.rank == 0:
+            print(json.dumps({"check_ranks": True, "world": ranks.world, "max_ms": worst, "sum_gb": total,
+                              "value": total / (worst * 1e-3)}), flush=True)
+        ranks.close()
+        return 0
     if args.impl == "reference":
         return run_reference(args, ranks)
     return run_ours(args, ranks)

@@ -175,7 +175,7 @@ SA_API void sideaware_elementwise(int kernel_id, size_t num_bytes,
             return;
         }
         sa_prepare_launch(dev, (uint64_t)in0, num_vecs, parallel_groups, forced_per_side, false, &s, &grid, &threads);
-        e = sa_launch_memcpy(s, grid, threads, out0, in0, (cudaStream_t)stream);
+        e = sa_launch_memcpy(s, dev->side_table, grid, threads, out0, in0, (cudaStream_t)stream);
         if (e != cudaSuccess) sa_set_error("sideaware_memcpy launch: %s", cudaGetErrorString(e));
         return;
     }
@@ -234,8 +234,9 @@ SA_API sideaware_status_t sideaware_rope_forward(void* qkv, const float* freqs_c
     const uint64_t num_vecs = (uint64_t)B * T * sh.vecs_per_row;
     SaSched s;
     int grid = 0, threads = 0;
-    sa_prepare_launch(dev, (uint64_t)qkv, num_vecs, 0, 0, false, &s, &grid, &threads);
-    cudaError_t e = sa_launch_rope(s, grid, threads, qkv, freqs_cis, sh, dtype == 1, (cudaStream_t)stream);
+    // 768 threads per block: the rotation needs ~70 registers, measured faster than 1024 threads with spills
+    sa_prepare_launch(dev, (uint64_t)qkv, num_vecs, 3, 0, false, &s, &grid, &threads);
+    cudaError_t e = sa_launch_rope(s, dev->side_table, grid, threads, qkv, freqs_cis, sh, dtype == 1, (cudaStream_t)stream);
     if (e != cudaSuccess) sa_set_error("sideaware_rope_forward launch: %s", cudaGetErrorString(e));
     return e;
 }
@@ -255,7 +256,7 @@ SA_API sideaware_status_t sideaware_silu_mul_bf16(void* out, const void* a, cons
     SaSched s;
     int grid = 0, threads = 0;
     sa_prepare_launch(dev, (uint64_t)a, n / 8, 0, 0, false, &s, &grid, &threads);
-    cudaError_t e = sa_launch_silu_mul(s, grid, threads, out, a, b, scale, (cudaStream_t)stream);
+    cudaError_t e = sa_launch_silu_mul(s, dev->side_table, grid, threads, out, a, b, scale, (cudaStream_t)stream);
     if (e != cudaSuccess) sa_set_error("sideaware_silu_mul_bf16 launch: %s", cudaGetErrorString(e));
     return e;
 }
@@ -448,17 +449,16 @@ SA_API sideaware_status_t sideaware_memcpy_noalloc(void* out, const void* in, si
     const int warps = 32;
     sa_sched_geometry(s, (uint64_t)in, num_bytes / 16, (uint32_t)(num_sms * warps / 2));
     int grid = num_sms;
-    int need_blocks = (int)((2ull * s.num_tickets + warps - 1) / warps);
-    if (need_blocks < 1) need_blocks = 1;
-    if (need_blocks < grid) grid = need_blocks;
-    s.total_warps = (uint32_t)(grid * warps);
+    sa_sched_grid(s, num_sms, warps, &grid);
     s.placement = SA_PLACE_UNAWARE;
+    SaSideTable sides;
+    std::memset(&sides, 0, sizeof(sides));
     if (dev && dev->full_hash) {
         s.hash = dev->full_hash;
         s.placement = (uint32_t)sa_config().placement.load();
-        std::memcpy(s.side_of_sm, dev->topo.side_index, SA_MAX_SM);
+        sides = dev->side_table;
     }
-    cudaError_t e = sa_launch_memcpy_noalloc(s, device, grid, warps * 32, out, in, (cudaStream_t)stream);
+    cudaError_t e = sa_launch_memcpy_noalloc(s, sides, device, grid, warps * 32, out, in, (cudaStream_t)stream);
     if (e != cudaSuccess) sa_set_error("sideaware_memcpy_noalloc: %s", cudaGetErrorString(e));
     return e;
 }

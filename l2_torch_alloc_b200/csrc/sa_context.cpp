@@ -177,6 +177,7 @@ bool init_device(SaDevice* dev) {
     if (!dev->topo.hash_usable)
         std::fprintf(stderr, "sideaware: device %d: no usable side hash found (hash 0x%x, %d validation errors, confidence %.2f); "
                              "kernels run side-unaware\n", dev->id, dev->topo.hash, dev->topo.validation_errors, dev->topo.confidence);
+    std::memcpy(dev->side_table.side_of_sm, dev->topo.side_index, SA_MAX_SM);
     dev->summary[0] = dev->topo.num_sms;
     dev->summary[1] = dev->topo.count[0];
     dev->summary[2] = dev->topo.count[1];
@@ -250,23 +251,23 @@ void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, in
     std::memset(s, 0, sizeof(*s));
     int groups = parallel_groups > 0 ? parallel_groups : 4;
     if (groups > 4) groups = 4;
+    static const int forced_groups = [] { // tuning aid: SIDEAWARE_GROUPS = 256-thread groups per block
+        const char* e = std::getenv("SIDEAWARE_GROUPS");
+        int v = e ? std::atoi(e) : 0;
+        return (v >= 1 && v <= 4) ? v : 0;
+    }();
+    if (forced_groups && forced_groups < groups) groups = forced_groups; // may only lower a kernel's own choice
     int warps = groups * 8;
     int g = dev->topo.num_sms;
     if (forced_per_side > 0 && 2 * forced_per_side < g) g = 2 * forced_per_side;
     s->dc_per_ticket = 0;
     sa_sched_geometry(*s, track_addr, num_vecs, (uint32_t)(g * warps / 2));
-    // small arrays: no more blocks than there are tickets to hand out
-    uint64_t need_warps = 2ull * s->num_tickets;
-    int need_blocks = (int)((need_warps + warps - 1) / warps);
-    if (need_blocks < 1) need_blocks = 1;
-    if (need_blocks < g) g = need_blocks;
+    sa_sched_grid(*s, g, warps, &g);
     s->tickets = sa_probe_ticket_slot(dev->probe);
     s->hash = dev->full_hash;
     int placement = sa_config().placement.load();
     s->placement = dev->full_hash ? (uint32_t)placement : (uint32_t)SA_PLACE_UNAWARE;
     s->reverse = reverse ? 1u : 0u;
-    s->total_warps = (uint32_t)(g * warps);
-    std::memcpy(s->side_of_sm, dev->topo.side_index, SA_MAX_SM);
     *grid = g;
     *threads = warps * 32;
     dev->launches.fetch_add(1);

@@ -40,6 +40,7 @@ struct SaDevice {
     std::unique_ptr<SaAllocator> alloc;
     int summary[5] = {0, 0, 0, 0, 0};
     uint32_t full_hash = 0; // hash | 1 << 21 when usable, else 0
+    SaSideTable side_table; // bit 0 of each byte = side of the SM; passed to every kernel
     std::atomic<unsigned long long> small_allocs{0}, launches{0}, jit_compiles{0};
     SaJitDeviceCache* jit = nullptr;
     std::mutex jit_mu;

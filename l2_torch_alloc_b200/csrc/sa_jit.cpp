@@ -237,19 +237,20 @@ cudaError_t sa_jit_launch(SaDevice* dev, int id, bool wide, const SaSched& sched
     SaSched s = sched;
     ArgsNarrow an;
     ArgsWide aw;
-    void* params[2] = {&s, nullptr};
+    SaSideTable sides = dev->side_table;
+    void* params[3] = {&s, &sides, nullptr};
     if (wide) {
         aw.num_vecs = (long long)num_vecs;
         for (int i = 0; i < 4; ++i) { aw.out[i] = out[i]; aw.in[i] = in[i]; }
         aw.mem = (int*)mem;
         aw.val = val;
-        params[1] = &aw;
+        params[2] = &aw;
     } else {
         an.num_vecs = (int)num_vecs;
         for (int i = 0; i < 4; ++i) { an.out[i] = out[i]; an.in[i] = in[i]; }
         an.mem = (int*)mem;
         an.val = val;
-        params[1] = &an;
+        params[2] = &an;
     }
     CUresult r = dev->drv->LaunchKernel(fn, (unsigned)grid, 1, 1, (unsigned)threads, 1, 1, 0, (CUstream)stream, params, nullptr);
     if (r != CUDA_SUCCESS) {

@@ -124,6 +124,7 @@ struct SaJitArgs {
 };
 
 extern "C" __global__ LAUNCH_BOUNDS void sideaware_elementwise(const __grid_constant__ SaSched launch,
+                                                               const __grid_constant__ SaSideTable sides,
                                                                const __grid_constant__ SaJitArgs a) {
     // geometry follows the array that is moved in 16-byte vectors
     SaSched s = launch;
@@ -142,12 +143,11 @@ extern "C" __global__ LAUNCH_BOUNDS void sideaware_elementwise(const __grid_cons
     const sa_pack<i3>* const pi3 = (const sa_pack<i3>*)a.in[3];
     const sa_u32 lane = sa_lane();
 
-    sa_for_each_chunk(s, [&](sa_u64 first_vec) {
+    sa_for_each_chunk(s, sides, [&](sa_u64 first_vec) {
         const bool whole = first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end;
+        const size_type v0 = (size_type)(first_vec - s.lead) + (size_type)lane; // may be "negative" in the first chunk
 #pragma unroll 1
         for (int b = 0; b < SA_VEC_PER_LANE / sa_batch; ++b) {
-            size_type vidx[sa_batch];
-            size_type ix[sa_batch][4];
             bool live[sa_batch];
             sa_pack<i0> r0[sa_batch];
             sa_pack<i1> r1[sa_batch];
@@ -155,43 +155,47 @@ extern "C" __global__ LAUNCH_BOUNDS void sideaware_elementwise(const __grid_cons
             sa_pack<i3> r3[sa_batch];
 #pragma unroll
             for (int j = 0; j < sa_batch; ++j) {
-                sa_u64 v = first_vec + (sa_u64)(b * sa_batch + j) * 32u + lane;
-                live[j] = whole || (v >= s.lead && v < s.end);
-                vidx[j] = (size_type)(v - s.lead);
+                const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
+                live[j] = whole || (first_vec + (sa_u64)((b * sa_batch + j) * 32) + lane >= s.lead &&
+                                    first_vec + (sa_u64)((b * sa_batch + j) * 32) + lane < s.end);
                 if (live[j]) {
-                    ix[j][0] = ix[j][1] = ix[j][2] = ix[j][3] = 0;
-                    bool skip = indexing(vidx[j], vec_size, ix[j][0], ix[j][1], ix[j][2], ix[j][3], a.mem, a.val);
-                    live[j] = !skip;
-                }
-                if (live[j]) {
-                    sa_load<input_evict[0]>(r0[j], pi0, ix[j][0]);
-                    sa_load<input_evict[1]>(r1[j], pi1, ix[j][1]);
-                    sa_load<input_evict[2]>(r2[j], pi2, ix[j][2]);
-                    sa_load<input_evict[3]>(r3[j], pi3, ix[j][3]);
+                    size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
+                    live[j] = !indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
+                    if (live[j]) {
+                        sa_load<input_evict[0]>(r0[j], pi0, x0);
+                        sa_load<input_evict[1]>(r1[j], pi1, x1);
+                        sa_load<input_evict[2]>(r2[j], pi2, x2);
+                        sa_load<input_evict[3]>(r3[j], pi3, x3);
+                    }
                 }
             }
 #pragma unroll
             for (int j = 0; j < sa_batch; ++j) {
                 if (live[j]) {
+                    const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
                     sa_pack<o0> w0;
                     sa_pack<o1> w1;
                     sa_pack<o2> w2;
                     sa_pack<o3> w3;
-                    vector_op(vidx[j], vec_size, w0.v, w1.v, w2.v, w3.v, r0[j].v, r1[j].v, r2[j].v, r3[j].v, a.mem, a.val);
-                    sa_store(po0, vidx[j], w0);
-                    sa_store(po1, vidx[j], w1);
-                    sa_store(po2, vidx[j], w2);
-                    sa_store(po3, vidx[j], w3);
+                    vector_op(vidx, vec_size, w0.v, w1.v, w2.v, w3.v, r0[j].v, r1[j].v, r2[j].v, r3[j].v, a.mem, a.val);
+                    sa_store(po0, vidx, w0);
+                    sa_store(po1, vidx, w1);
+                    sa_store(po2, vidx, w2);
+                    sa_store(po3, vidx, w3);
                 }
             }
 #ifdef DISCARD_INPUTS
+            // after the stores of the batch; the input positions are computed again rather than kept
 #pragma unroll
             for (int j = 0; j < sa_batch; ++j) {
                 if (live[j]) {
-                    sa_discard(pi0, ix[j][0], input_discard[0]);
-                    sa_discard(pi1, ix[j][1], input_discard[1]);
-                    sa_discard(pi2, ix[j][2], input_discard[2]);
-                    sa_discard(pi3, ix[j][3], input_discard[3]);
+                    const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
+                    size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
+                    indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
+                    sa_discard(pi0, x0, input_discard[0]);
+                    sa_discard(pi1, x1, input_discard[1]);
+                    sa_discard(pi2, x2, input_discard[2]);
+                    sa_discard(pi3, x3, input_discard[3]);
                 }
             }
 #endif

@@ -29,9 +29,10 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 // memcpy
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kMaxThreads, 1)
-sa_memcpy_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ dst, const uint4* __restrict__ src) {
+sa_memcpy_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSideTable sides,
+                 uint4* __restrict__ dst, const uint4* __restrict__ src) {
     const uint32_t lane = sa_lane();
-    sa_for_each_chunk(s, [&](uint64_t first_vec) {
+    sa_for_each_chunk(s, sides, [&](uint64_t first_vec) {
         if (first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end) {
             const uint64_t e = first_vec - s.lead + lane;
             const uint4* p = src + e;
@@ -66,20 +67,20 @@ template <bool BF16>
 __device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab) {
     uint4 out;
     if constexpr (BF16) {
-        // 8 bf16 = 4 pairs, table = 4 x (cos, sin) = two float4
-        const float4 t0 = __ldg(tab), t1 = __ldg(tab + 1);
-        const float cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-        const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            float x = __uint_as_float(w[p] << 16), y = __uint_as_float(w[p] & 0xffff0000u);
+        // 8 bf16 = 4 pairs, table = 4 x (cos, sin) = two float4, consumed one after the other
+        auto pair = [](uint32_t w, float c, float s) {
+            float x = __uint_as_float(w << 16), y = __uint_as_float(w & 0xffff0000u);
             float ox, oy;
-            rotate(x, y, cs[2 * p], cs[2 * p + 1], ox, oy);
+            rotate(x, y, c, s, ox, oy);
             __nv_bfloat162 b = __floats2bfloat162_rn(ox, oy);
-            o[p] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        out = make_uint4(o[0], o[1], o[2], o[3]);
+            return *reinterpret_cast<uint32_t*>(&b);
+        };
+        const float4 t0 = __ldg(tab);
+        out.x = pair(in.x, t0.x, t0.y);
+        out.y = pair(in.y, t0.z, t0.w);
+        const float4 t1 = __ldg(tab + 1);
+        out.z = pair(in.z, t1.x, t1.y);
+        out.w = pair(in.w, t1.z, t1.w);
     } else {
         // 4 floats = 2 pairs, table = one float4
         const float4 t = __ldg(tab);
@@ -103,12 +104,13 @@ __device__ __forceinline__ bool rope_locate(const SaRopeShape& sh, uint64_t e, u
     return true;
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(kMaxThreads, 1)
-sa_rope_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ x, const float4* __restrict__ table,
+template <bool BF16, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1)
+sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSideTable sides,
+               uint4* __restrict__ x, const float4* __restrict__ table,
                const __grid_constant__ SaRopeShape sh) {
     const uint32_t lane = sa_lane();
-    sa_for_each_chunk(s, [&](uint64_t first_vec) {
+    sa_for_each_chunk(s, sides, [&](uint64_t first_vec) {
         if (first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end && sh.vecs_per_row >= SA_CHUNK_VECS) {
             // whole chunk: one 64-bit division per chunk, then 32-bit bookkeeping per vector
             const uint64_t e0 = first_vec - s.lead;
@@ -117,23 +119,31 @@ sa_rope_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ x, const f
             const uint32_t tok0 = (uint32_t)(row0 % sh.T);
             uint4* p = x + e0 + lane;
             uint4 v[SA_VEC_PER_LANE];
-            uint32_t tab_idx[SA_VEC_PER_LANE];
-            bool live[SA_VEC_PER_LANE];
-#pragma unroll
-            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
-                uint32_t r = r0 + k * 32, tok = tok0;
+            // position of vector k of this lane inside its token row; recomputed (not kept) for the
+            // second loop to stay inside the 64-register budget of a 1024-thread block
+            auto locate = [&](int k, uint32_t& r, uint32_t& tok) {
+                r = r0 + k * 32;
+                tok = tok0;
                 if (r >= sh.vecs_per_row) { // a chunk is shorter than a row: at most one wrap
                     r -= sh.vecs_per_row;
                     tok = (tok + 1 == sh.T) ? 0 : tok + 1;
                 }
-                live[k] = r < sh.rotated_vecs;
-                uint32_t pos = sh.head_shift >= 0 ? (r & (sh.vecs_per_head - 1)) : (r % sh.vecs_per_head);
-                tab_idx[k] = tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec;
-                if (live[k]) v[k] = ld_stream(p + k * 32);
+            };
+#pragma unroll
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                uint32_t r, tok;
+                locate(k, r, tok);
+                if (r < sh.rotated_vecs) v[k] = ld_stream(p + k * 32);
             }
 #pragma unroll
-            for (int k = 0; k < SA_VEC_PER_LANE; ++k)
-                if (live[k]) p[k * 32] = rope_vec<BF16>(v[k], table + tab_idx[k]);
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                uint32_t r, tok;
+                locate(k, r, tok);
+                if (r < sh.rotated_vecs) {
+                    uint32_t pos = sh.head_shift >= 0 ? (r & (sh.vecs_per_head - 1)) : (r % sh.vecs_per_head);
+                    p[k * 32] = rope_vec<BF16>(v[k], table + tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec);
+                }
+            }
         } else {
 #pragma unroll 1
             for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
@@ -165,10 +175,11 @@ __device__ __forceinline__ uint4 silu_mul_vec(uint4 a, uint4 b, float scale) {
 }
 
 __global__ void __launch_bounds__(kMaxThreads, 1)
-sa_silu_mul_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ out, const uint4* __restrict__ a,
+sa_silu_mul_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSideTable sides,
+                   uint4* __restrict__ out, const uint4* __restrict__ a,
                    const uint4* __restrict__ b, float scale) {
     const uint32_t lane = sa_lane();
-    sa_for_each_chunk(s, [&](uint64_t first_vec) {
+    sa_for_each_chunk(s, sides, [&](uint64_t first_vec) {
         if (first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end) {
             const uint64_t e = first_vec - s.lead + lane;
 #pragma unroll
@@ -195,21 +206,25 @@ sa_silu_mul_kernel(const __grid_constant__ SaSched s, uint4* __restrict__ out, c
 
 } // namespace
 
-cudaError_t sa_launch_memcpy(const SaSched& s, int grid, int threads, void* dst, const void* src, cudaStream_t stream) {
-    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)dst, (const uint4*)src);
+cudaError_t sa_launch_memcpy(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* dst, const void* src, cudaStream_t stream) {
+    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, sides, (uint4*)dst, (const uint4*)src);
     return cudaGetLastError();
 }
 
-cudaError_t sa_launch_rope(const SaSched& s, int grid, int threads, void* x, const float* table,
+cudaError_t sa_launch_rope(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* x, const float* table,
                            const SaRopeShape& sh, bool bf16, cudaStream_t stream) {
-    if (bf16) sa_rope_kernel<true><<<grid, threads, 0, stream>>>(s, (uint4*)x, (const float4*)table, sh);
-    else sa_rope_kernel<false><<<grid, threads, 0, stream>>>(s, (uint4*)x, (const float4*)table, sh);
+    // at most 768 threads per block: that leaves 85 registers per thread (the bf16 rotation needs
+    // ~72; a 1024-thread block would cap it at 64 and spill), and 24 warps x 4 KiB still keep
+    // 96 KiB in flight per SM
+    if (threads > 768) return cudaErrorInvalidConfiguration;
+    if (bf16) sa_rope_kernel<true, 768><<<grid, threads, 0, stream>>>(s, sides, (uint4*)x, (const float4*)table, sh);
+    else sa_rope_kernel<false, 768><<<grid, threads, 0, stream>>>(s, sides, (uint4*)x, (const float4*)table, sh);
     return cudaGetLastError();
 }
 
-cudaError_t sa_launch_silu_mul(const SaSched& s, int grid, int threads, void* out, const void* a, const void* b,
+cudaError_t sa_launch_silu_mul(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream) {
-    sa_silu_mul_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
+    sa_silu_mul_kernel<<<grid, threads, 0, stream>>>(s, sides, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
     return cudaGetLastError();
 }
 
@@ -234,7 +249,7 @@ unsigned int* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
 // kernel could use) and keeps it.  Every call then zeroes the counters on `stream` before
 // the kernel runs, because the array is shared by all calls and keeps whatever the last
 // one left behind.
-cudaError_t sa_launch_memcpy_noalloc(SaSched s, int device, int grid, int threads, void* dst, const void* src,
+cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int device, int grid, int threads, void* dst, const void* src,
                                      cudaStream_t stream) {
     if (device < 0 || device >= kNoAllocMaxDevices) return cudaErrorInvalidDevice;
     unsigned int* scratch = nullptr;
@@ -251,6 +266,6 @@ cudaError_t sa_launch_memcpy_noalloc(SaSched s, int device, int grid, int thread
     cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(unsigned int) * SA_NOALLOC_SCRATCH_WORDS, stream);
     if (e != cudaSuccess) return e;
     s.tickets = scratch;
-    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, (uint4*)dst, (const uint4*)src);
+    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, sides, (uint4*)dst, (const uint4*)src);
     return cudaGetLastError();
 }

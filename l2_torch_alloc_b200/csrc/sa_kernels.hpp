@@ -16,11 +16,11 @@ struct SaRopeShape {
     int32_t head_shift;          // log2(vecs_per_head) if it is a power of two, else -1
 };
 
-cudaError_t sa_launch_memcpy(const SaSched& s, int grid, int threads, void* dst, const void* src, cudaStream_t stream);
-cudaError_t sa_launch_rope(const SaSched& s, int grid, int threads, void* x, const float* table,
+cudaError_t sa_launch_memcpy(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* dst, const void* src, cudaStream_t stream);
+cudaError_t sa_launch_rope(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* x, const float* table,
                            const SaRopeShape& sh, bool bf16, cudaStream_t stream);
-cudaError_t sa_launch_silu_mul(const SaSched& s, int grid, int threads, void* out, const void* a, const void* b,
+cudaError_t sa_launch_silu_mul(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream);
 // Same kernel as sa_launch_memcpy with its ticket counters in a static device array (no allocation).
-cudaError_t sa_launch_memcpy_noalloc(SaSched s, int device, int grid, int threads, void* dst, const void* src,
+cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int device, int grid, int threads, void* dst, const void* src,
                                      cudaStream_t stream);

@@ -43,6 +43,7 @@ def build(force: bool = False) -> None:
     ref_src = os.environ.get("SIDEAWARE_REFERENCE_TREE", "/root/reference")
     if os.path.exists(os.path.join(ref_src, "example_llmc_rope.cu")) and (
         force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_rope.so"))
+        or not os.path.exists(os.path.join(_HERE, "_ref", "sideaware_reference.so"))
     ):
         subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={ref_src}"], stdout=subprocess.DEVNULL)
 

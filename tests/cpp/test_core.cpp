@@ -102,6 +102,24 @@ static void test_sched() {
         uint32_t per = (uint32_t)(rng() % 9); // 0 = automatic
         sched_case(addr, n, hashes[rng() % 4], (uint32_t)(rng() % 3), rng() & 1, 1 + rng() % 3000, per);
     }
+    // hand-out policy: the opening batches never ask for more warps than a block has, always deal
+    // at least one ticket, cover small arrays completely on a balanced device, and never launch more
+    // blocks than there are tickets
+    for (uint64_t n : {1ull, 300ull, 512ull * 100, 4ull << 16, 1ull << 20, 4ull << 20, 1ull << 24, 1ull << 26, 1ull << 30}) {
+        for (int warps : {8, 16, 24, 32}) {
+            SaSched s;
+            std::memset(&s, 0, sizeof(s));
+            sa_sched_geometry(s, 0x7f0000000000ull, n, 74 * warps);
+            int grid = 0;
+            sa_sched_grid(s, 148, warps, &grid);
+            CHECK(grid >= 1 && grid <= 148 && (uint64_t)grid <= 2ull * s.num_tickets);
+            CHECK(s.active_warps >= 1 && s.active_warps <= (uint32_t)warps && s.share >= 1);
+            CHECK(s.total_blocks == (uint32_t)grid);
+            uint64_t dealt = (uint64_t)((grid + 1) / 2) * s.active_warps * s.share;
+            if (!s.dynamic) CHECK(dealt >= s.num_tickets);
+            if (s.dynamic) CHECK(dealt < s.num_tickets && s.active_warps == (uint32_t)warps);
+        }
+    }
     std::printf("sched: done\n");
 }
 

@@ -1,0 +1,38 @@
+"""This library's memcpy next to the REFERENCE's own GPU path on the same B200: the reference
+sideaware.cu compiled in place into oracle/_ref/sideaware_reference.so (its allocator, its
+NVRTC-JIT-ed kernel for sm_100), timed by the same script in separate processes.
+Skipped where the compiled reference is not present."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "oracle", "_ref", "sideaware_reference.so")
+OURS = os.path.join(ROOT, "l2_torch_alloc_b200", "sideaware.so")
+
+
+def run(lib, sizes):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "memcpy_timing_script.py"), lib, sizes],
+                       capture_output=True, text=True, timeout=600, cwd=ROOT)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert lines, r.stdout[-2000:] + r.stderr[-2000:]
+    return json.loads(lines[-1][7:])
+
+
+@pytest.mark.skipif(not os.path.exists(REF), reason="compiled reference not present")
+def test_memcpy_not_slower_than_the_reference_kernel():
+    sizes = f"{64 << 20},{1 << 30}"
+    ref = run(REF, sizes)
+    ours = run(OURS, sizes)
+    print("reference:", json.dumps(ref))
+    print("ours:     ", json.dumps(ours))
+    assert ref["summary"][0] == ours["summary"][0]
+    for n in ref["sizes"]:
+        assert ref["sizes"][n]["exact"] and ours["sizes"][n]["exact"]
+    one_gib = str(1 << 30)
+    assert ours["sizes"][one_gib]["gbs"] >= 0.97 * ref["sizes"][one_gib]["gbs"]
