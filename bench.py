@@ -214,6 +214,8 @@ def load_cudart(torch):
     else:
         raise SystemExit("CUDA runtime library not found")
     rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+    rt.cudaMallocAsync.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t, ctypes.c_void_p]
+    rt.cudaFreeAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     return rt
 
 
@@ -303,6 +305,105 @@ def run_reference(args, ranks):
     ranks.close()
     return 0
 
+
+
+# ---------------------------------------------------------------------------
+# allocator churn and power (extras, rank 0 at N = 1)
+# ---------------------------------------------------------------------------
+def allocator_churn(lib, rt, dev, sp, ops, use_runtime_pool=False):
+    """`ops` seeded malloc/free calls, sizes log-uniform 4 KiB .. 2 GiB rounded up to 16 B, live set capped
+    at 32 GiB, through sideaware_malloc_auto / sideaware_free_auto (what torch's pluggable allocator calls),
+    or through cudaMallocAsync / cudaFreeAsync for comparison."""
+    import ctypes
+    import numpy as np
+    rng = np.random.default_rng(0xB200 + 5)
+    live, live_bytes, peak = [], 0, 0
+    t_malloc_small, t_malloc_large, t_free = [], [], []
+    p = ctypes.c_void_p()
+    t_start = time.perf_counter()
+    for _ in range(ops):
+        if live and (live_bytes > (32 << 30) or rng.random() < 0.45):
+            ptr, size = live.pop(int(rng.integers(len(live))))
+            t0 = time.perf_counter_ns()
+            if use_runtime_pool:
+                rt.cudaFreeAsync(ptr, sp)
+            else:
+                lib.sideaware_free_auto(ptr, size, dev, sp)
+            t_free.append(time.perf_counter_ns() - t0)
+            live_bytes -= size
+        else:
+            size = int(np.exp(rng.uniform(np.log(4096), np.log(2 << 30))))
+            size = (size + 15) // 16 * 16
+            t0 = time.perf_counter_ns()
+            if use_runtime_pool:
+                rc = rt.cudaMallocAsync(ctypes.byref(p), size, sp)
+                ptr = p.value if rc == 0 else None
+            else:
+                ptr = lib.sideaware_malloc_auto(size, dev, sp)
+            dt = time.perf_counter_ns() - t0
+            if not ptr:
+                continue
+            (t_malloc_large if size >= (8 << 20) else t_malloc_small).append(dt)
+            live.append((ptr, size))
+            live_bytes += size
+            peak = max(peak, live_bytes)
+    for ptr, size in live:
+        if use_runtime_pool:
+            rt.cudaFreeAsync(ptr, sp)
+        else:
+            lib.sideaware_free_auto(ptr, size, dev, sp)
+    elapsed = time.perf_counter() - t_start
+
+    def pct(v, q):
+        return float(np.percentile(v, q)) / 1e3 if v else None
+
+    return {"ops": ops, "ops_per_s": ops / elapsed, "seconds": elapsed, "peak_live_gib": peak / 2**30,
+            "malloc_small_us_p50": pct(t_malloc_small, 50), "malloc_small_us_p99": pct(t_malloc_small, 99),
+            "malloc_large_us_p50": pct(t_malloc_large, 50), "malloc_large_us_p99": pct(t_malloc_large, 99),
+            "free_us_p50": pct(t_free, 50), "free_us_p99": pct(t_free, 99)}
+
+
+def power_run(torch, fn, nbytes, seconds, index):
+    """Runs fn() back to back for about `seconds` and samples board power through NVML."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+    except Exception:  # noqa: BLE001
+        return None
+    samples, stop = [], threading.Event()
+
+    def sampler():
+        while not stop.is_set():
+            try:
+                samples.append(pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.01)
+
+    for _ in range(20):
+        fn()
+    torch.cuda.synchronize()
+    th = threading.Thread(target=sampler, daemon=True)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    th.start()
+    t0 = time.perf_counter()
+    n = 0
+    start.record()
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(50):
+            fn()
+        n += 50
+        torch.cuda.synchronize()
+    end.record()
+    torch.cuda.synchronize()
+    stop.set()
+    th.join()
+    ms = start.elapsed_time(end)
+    tail = samples[len(samples) // 3:] or samples  # the power reading lags: use the settled part
+    watts = statistics.mean(tail) if tail else None
+    rate = n * nbytes / (ms * 1e-3) / 1e9
+    return {"watts": watts, "gbs": rate, "joule_per_gb": (watts / rate) if watts else None, "samples": len(samples)}
 
 # ---------------------------------------------------------------------------
 # GPU arm
@@ -402,6 +503,17 @@ def run_ours(args, ranks):
         del t_dst
         extra["memcpy_comparison"] = comp
 
+        # ---- board power while copying (the reference's headline claim is power, sideaware.cu:4) ----
+        if ranks.world == 1 and args.power_seconds > 0:
+            power = {}
+            for mode in ("aware", "unaware"):
+                sa.set_placement(mode)
+                power[f"kernel_{mode}"] = power_run(torch, step, 2 * MEMCPY_BYTES, args.power_seconds, dev)
+            sa.set_placement("aware")
+            power["cudaMemcpyAsync_d2d"] = power_run(torch, lambda: rt.cudaMemcpyAsync(dst, src, MEMCPY_BYTES, 3, sp),
+                                                     2 * MEMCPY_BYTES, args.power_seconds, dev)
+            extra["power"] = power
+
         # ---- size sweep 4 MiB .. 8 GiB (threshold lowered so 4 MiB blocks are side-aware too) ----
         sweep = {}
         lib.sideaware_alloc_threshold(4 << 20)
@@ -492,6 +604,17 @@ def run_ours(args, ranks):
         if sa.error_count():
             functor["errors"] = sa.last_error()
 
+    churn = None
+    if ranks.rank == 0 and ranks.world == 1 and args.churn_ops > 0:
+        lib.sideaware_release_unused()
+        torch.cuda.synchronize()
+        churn = {"sideaware": allocator_churn(lib, rt, dev, sp, args.churn_ops)}
+        churn["sideaware"]["stats"] = sa.stats()
+        lib.sideaware_release_unused()
+        torch.cuda.synchronize()
+        churn["cudaMallocAsync"] = allocator_churn(lib, rt, dev, sp, args.churn_ops, use_runtime_pool=True)
+        torch.cuda.synchronize()
+
     line = None
     if ranks.rank == 0:
         cpu = None
@@ -509,7 +632,8 @@ def run_ours(args, ranks):
                        "bytes": MEMCPY_BYTES, "l2": "inputs larger than L2 (2 GiB touched per step vs 126 MB)",
                        "parallelism": f"{ranks.world} independent replicas, no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * ranks.world,
-            "clocks": clocks.report(), "topology": summary, "rope": rope, "functor": functor, **extra,
+            "clocks": clocks.report(), "topology": summary, "rope": rope, "functor": functor,
+            "allocator_churn": churn, **extra,
         }
         print(json.dumps(line), flush=True)
     ranks.close()
@@ -522,6 +646,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--churn-ops", type=int, default=10000, help="allocator churn operations (N = 1 only; 0 = skip)")
+    ap.add_argument("--power-seconds", type=float, default=2.0, help="length of each power sampling loop (0 = skip)")
     ap.add_argument("--check-ranks", action="store_true",
                     help="exercise only the rank plumbing (barrier, max/sum over ranks, rank 0 prints); needs no GPU")
     args = ap.parse_args()

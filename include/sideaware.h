@@ -161,6 +161,11 @@ typedef struct sideaware_stats_t {
 } sideaware_stats_t;
 void sideaware_get_stats(sideaware_stats_t* out);
 
+/* Host time (ns) and call counts the allocator has spent in driver calls since load, by kind:
+ * [0] cuMemCreate [1] cuMemRelease [2] cuMemAddressReserve/Free [3] cuMemMap [4] cuMemUnmap
+ * [5] cuMemSetAccess [6] side probing [7] synchronisation.  For allocator tuning. */
+void sideaware_driver_call_times(unsigned long long ns_out[8], unsigned long long calls_out[8]);
+
 /* Raw discovery data of the current device (latency matrix etc.) as JSON text
  * owned by the library; for diagnostics. */
 const char* sideaware_topology_json(void);

@@ -68,6 +68,7 @@ SIGNATURES = {
     "sideaware_verify_chunk_sides": (_i, [_vp, _sz, _i, c.c_uint]),
     "sideaware_get_stats": (None, [c.POINTER(Stats)]),
     "sideaware_topology_json": (c.c_char_p, []),
+    "sideaware_driver_call_times": (None, [c.POINTER(c.c_ulonglong * 8), c.POINTER(c.c_ulonglong * 8)]),
     "sideaware_memcpy_noalloc": (_i, [_vp, _vp, _sz, _i, _vp]),
 }
 

@@ -62,6 +62,14 @@ class SideAware:
         self.lib.sideaware_get_stats(ctypes.byref(st))
         return st.as_dict()
 
+    def driver_call_times(self) -> dict:
+        """Host milliseconds and call counts the allocator spent in driver calls, by kind."""
+        ns = (ctypes.c_ulonglong * 8)()
+        calls = (ctypes.c_ulonglong * 8)()
+        self.lib.sideaware_driver_call_times(ctypes.byref(ns), ctypes.byref(calls))
+        names = ["create", "release", "reserve", "map", "unmap", "set_access", "probe", "sync"]
+        return {n: {"ms": ns[i] / 1e6, "calls": int(calls[i])} for i, n in enumerate(names)}
+
     def topology_json(self) -> str:
         return (self.lib.sideaware_topology_json() or b"{}").decode()
 

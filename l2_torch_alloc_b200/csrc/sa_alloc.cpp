@@ -8,10 +8,16 @@ static inline size_t round_to_pages(size_t size) {
     return (size + kSaPageBytes - 1) / kSaPageBytes * kSaPageBytes;
 }
 
+static inline int side_bit(uint64_t va) { return (int)((va >> kSaSideBit) & 1); }
+
 SaAllocator::~SaAllocator() {
     // Process teardown: the driver reclaims everything; touching it here could run
     // after the CUDA context is gone.
 }
+
+// ---------------------------------------------------------------------------
+// physical pages
+// ---------------------------------------------------------------------------
 
 // Creates `count` physical pages, learns their side through a temporary mapping and
 // files them in the pools.  Partial success is success (as sideaware.cu:1029-1033).
@@ -65,8 +71,8 @@ int SaAllocator::create_pages(int count, bool compressed, void* stream, const Sa
 }
 
 // Makes sure both pools can serve about half of `num_pages` each.  New pages land on
-// either side at random, hence the over-allocation (sideaware.cu:1064-1080) and up to
-// three rounds before the caller falls back to cross-side mapping.
+// either side at random, hence the over-allocation (sideaware.cu:1064-1080) and several
+// rounds before the caller falls back to cross-side mapping.
 int SaAllocator::top_up(size_t num_pages, bool compressed, void* stream, const SaAllocConfig& cfg) {
     int rc = 0;
     for (int round = 0; round < 4; ++round) {
@@ -88,34 +94,123 @@ int SaAllocator::top_up(size_t num_pages, bool compressed, void* stream, const S
     return 0;
 }
 
-bool SaAllocator::build_block(Block& b, size_t size, bool compressed, void* stream, const SaAllocConfig& cfg) {
-    b.bytes = round_to_pages(size);
-    b.requested = size;
-    b.compressed = compressed;
+void SaAllocator::release_pools() {
+    for (int c = 0; c < 2; ++c)
+        for (int s = 0; s < 2; ++s) {
+            for (auto& pg : pool_[c][s]) be_->release_page(pg.handle);
+            pool_[c][s].clear();
+        }
+}
+
+// ---------------------------------------------------------------------------
+// free runs
+// ---------------------------------------------------------------------------
+
+void SaAllocator::erase_free(std::map<uint64_t, Run>::iterator it) {
+    auto range = free_by_len_[it->second.seg->compressed].equal_range(it->second.pages);
+    for (auto j = range.first; j != range.second; ++j)
+        if (j->second == it->first) { free_by_len_[it->second.seg->compressed].erase(j); break; }
+    cached_bytes_ -= it->second.pages * kSaPageBytes;
+    free_.erase(it);
+}
+
+// Adds a free run and merges it with free neighbours of the same segment.
+void SaAllocator::insert_free(uint64_t va, Run run) {
+    auto merge = [](Run& into, const Run& other) {
+        into.pages += other.pages;
+        into.freed_seq = std::max(into.freed_seq, other.freed_seq);
+        if (other.mixed || other.stream != into.stream) into.mixed = true;
+    };
+    auto next = free_.lower_bound(va);
+    if (next != free_.end() && next->second.seg == run.seg && va + run.pages * kSaPageBytes == next->first) {
+        Run n = next->second;
+        erase_free(next);
+        merge(run, n);
+    }
+    auto prev = free_.lower_bound(va);
+    if (prev != free_.begin()) {
+        --prev;
+        if (prev->second.seg == run.seg && prev->first + prev->second.pages * kSaPageBytes == va) {
+            Run p = prev->second;
+            uint64_t pva = prev->first;
+            erase_free(prev);
+            merge(p, run);
+            run = p;
+            va = pva;
+        }
+    }
+    free_.emplace(va, run);
+    free_by_len_[run.seg->compressed].emplace(run.pages, va);
+    cached_bytes_ += run.pages * kSaPageBytes;
+}
+
+// Best fit: the shortest free run that can hold `pages` pages starting on side `phase`
+// (a run that starts on the other side needs one page more; that page stays free).
+uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, void* stream) {
+    auto& index = free_by_len_[compressed];
+    auto it = index.lower_bound(pages);
+    std::map<uint64_t, Run>::iterator pick = free_.end();
+    for (; it != index.end(); ++it) {
+        const bool aligned = side_bit(it->second) == phase;
+        if (aligned || it->first >= pages + 1) {
+            pick = free_.find(it->second);
+            break;
+        }
+    }
+    if (pick == free_.end()) return 0;
+    const uint64_t run_va = pick->first;
+    const Run run = pick->second;
+    erase_free(pick);
+    const size_t skip = side_bit(run_va) == phase ? 0 : 1;
+    const uint64_t base = run_va + skip * kSaPageBytes;
+    if (skip) {
+        Run head = run;
+        head.pages = 1;
+        insert_free(run_va, head);
+    }
+    const size_t tail = run.pages - skip - pages;
+    if (tail) {
+        Run rest = run;
+        rest.pages = tail;
+        insert_free(base + pages * kSaPageBytes, rest);
+    }
+    // work queued by the previous user(s) of these pages must be done before a different stream touches them
+    if (run.mixed) be_->device_sync();
+    else if (run.stream != stream) be_->stream_sync(run.stream);
+    Block b;
+    b.pages = pages;
+    b.seg = run.seg;
     b.stream = stream;
-    const size_t num_pages = b.bytes / kSaPageBytes;
+    live_.emplace(base, b);
+    live_bytes_ += pages * kSaPageBytes;
+    return base;
+}
 
-    top_up(num_pages, compressed, stream, cfg); // failure is handled below: we may still have enough pages
+// ---------------------------------------------------------------------------
+// growing and shrinking the mapped set
+// ---------------------------------------------------------------------------
+
+// Maps a new segment of exactly `pages` pages whose first page is on side `phase`
+// and hands all of it out as one block.
+uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg) {
+    top_up(pages, compressed, stream, cfg); // failure is handled below: we may still have enough pages
     auto& pools = pool_[compressed];
-    if (pools[0].size() + pools[1].size() < num_pages) return false;
+    if (pools[0].size() + pools[1].size() < pages) return 0;
 
-    // every block of this size starts on the same side, so equal-size buffers have equal side patterns
-    auto it = phase_.find(b.bytes);
-    if (it == phase_.end()) it = phase_.emplace(b.bytes, pools[0].size() >= pools[1].size() ? 0 : 1).first;
-    const int start_side = it->second;
-
+    std::unique_ptr<Segment> seg(new Segment());
+    seg->compressed = compressed;
+    seg->num_pages = pages;
     // one spare page of address space lets us pick the phase of bit 21
-    b.reserved_bytes = b.bytes + kSaPageBytes;
-    if (be_->reserve_va(&b.reserved, b.reserved_bytes)) return false;
-    b.base = b.reserved;
-    if ((int)((b.base >> kSaSideBit) & 1) != start_side) b.base += kSaPageBytes;
+    seg->reserved_bytes = (pages + 1) * kSaPageBytes;
+    if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
+    seg->base = seg->reserved;
+    if (side_bit(seg->base) != phase) seg->base += kSaPageBytes;
 
-    b.pages.clear();
-    b.pages.reserve(num_pages);
+    seg->pages.reserve(pages);
     bool ok = true;
-    for (size_t i = 0; i < num_pages && ok; ++i) {
-        uint64_t va = b.base + i * kSaPageBytes;
-        int want = (int)((va >> kSaSideBit) & 1);
+    for (size_t i = 0; i < pages && ok; ++i) {
+        uint64_t va = seg->base + i * kSaPageBytes;
+        int want = side_bit(va);
         int from = want;
         if (pools[from].empty()) {
             from ^= 1;
@@ -133,102 +228,126 @@ bool SaAllocator::build_block(Block& b, size_t size, bool compressed, void* stre
             ok = false;
             break;
         }
-        b.pages.push_back(pg);
+        seg->pages.push_back(pg);
     }
-    if (ok && be_->set_access(b.base, b.bytes)) ok = false;
+    if (ok && be_->set_access(seg->base, pages * kSaPageBytes)) ok = false;
     if (!ok) {
-        for (size_t i = 0; i < b.pages.size(); ++i) {
-            be_->unmap_page(b.base + i * kSaPageBytes);
-            pools[b.pages[i].side].push_back(b.pages[i]);
+        for (size_t i = 0; i < seg->pages.size(); ++i) {
+            be_->unmap_page(seg->base + i * kSaPageBytes);
+            pools[seg->pages[i].side].push_back(seg->pages[i]);
         }
-        b.pages.clear();
-        be_->free_va(b.reserved, b.reserved_bytes);
-        return false;
+        be_->free_va(seg->reserved, seg->reserved_bytes);
+        return 0;
     }
-    return true;
+    seg->mapped_pages = pages;
+    Block b;
+    b.pages = pages;
+    b.seg = seg.get();
+    b.stream = stream;
+    const uint64_t base = seg->base;
+    live_.emplace(base, b);
+    live_bytes_ += pages * kSaPageBytes;
+    segments_.push_back(std::move(seg));
+    return base;
 }
 
-void SaAllocator::unmap_block(Block& b) {
-    for (size_t i = 0; i < b.pages.size(); ++i) {
-        be_->unmap_page(b.base + i * kSaPageBytes);
-        pool_[b.compressed][b.pages[i].side].push_back(b.pages[i]);
+// Unmaps the pages of a free run (already removed from the free indices) and returns them to
+// the pools.  The hole stays reserved until the whole segment is unmapped.
+void SaAllocator::unmap_run(uint64_t va, const Run& run) {
+    Segment* seg = run.seg;
+    const size_t first = (size_t)((va - seg->base) / kSaPageBytes);
+    for (size_t i = 0; i < run.pages; ++i) {
+        Page& pg = seg->pages[first + i];
+        be_->unmap_page(va + i * kSaPageBytes);
+        pool_[seg->compressed][pg.side].push_back(pg);
+        pg.handle = 0;
     }
-    b.pages.clear();
-    be_->free_va(b.reserved, b.reserved_bytes);
+    seg->mapped_pages -= run.pages;
+    if (seg->mapped_pages == 0) {
+        be_->free_va(seg->reserved, seg->reserved_bytes);
+        for (size_t i = 0; i < segments_.size(); ++i)
+            if (segments_[i].get() == seg) {
+                segments_[i] = std::move(segments_.back());
+                segments_.pop_back();
+                break;
+            }
+    }
 }
 
 void SaAllocator::trim_locked(size_t start, size_t end) {
     if (cached_bytes_ <= start || cached_bytes_ == 0) return;
-    be_->device_sync(); // cached blocks may still be in use by queued work
+    be_->device_sync(); // freed pages may still be in use by queued work
     st_.trims++;
-    while (cached_bytes_ > end) {
-        std::vector<Block>* oldest_vec = nullptr;
-        size_t oldest_idx = 0;
-        uint64_t oldest = ~0ull;
-        for (auto& kv : cache_)
-            for (size_t i = 0; i < kv.second.size(); ++i)
-                if (kv.second[i].freed_seq < oldest) { oldest = kv.second[i].freed_seq; oldest_vec = &kv.second; oldest_idx = i; }
-        if (!oldest_vec) break;
-        Block b = std::move((*oldest_vec)[oldest_idx]);
-        oldest_vec->erase(oldest_vec->begin() + oldest_idx);
-        cached_bytes_ -= b.bytes;
-        unmap_block(b);
+    // least recently freed first
+    std::vector<std::pair<uint64_t, uint64_t>> order; // (freed_seq, va)
+    order.reserve(free_.size());
+    for (auto& kv : free_) order.emplace_back(kv.second.freed_seq, kv.first);
+    std::sort(order.begin(), order.end());
+    for (auto& o : order) {
+        if (cached_bytes_ <= end) break;
+        auto it = free_.find(o.second);
+        if (it == free_.end()) continue;
+        const uint64_t va = it->first;
+        const Run run = it->second;
+        erase_free(it);
+        unmap_run(va, run);
     }
     be_->device_sync();
+}
+
+// ---------------------------------------------------------------------------
+// public operations
+// ---------------------------------------------------------------------------
+
+// Blocks of one page-rounded size always start on the same side.  A size seen for the first
+// time takes the side that needs no skipped page in the best-fitting free run, else the side
+// with more pooled pages (the reference's rule, sideaware.cu:1084-1088).
+int SaAllocator::choose_phase(size_t bytes, size_t pages, bool compressed) {
+    auto it = phase_.find(bytes);
+    if (it != phase_.end()) return it->second;
+    int phase;
+    auto fit = free_by_len_[compressed].lower_bound(pages);
+    if (fit != free_by_len_[compressed].end()) phase = side_bit(fit->second);
+    else phase = pool_[compressed][0].size() >= pool_[compressed][1].size() ? 0 : 1;
+    phase_.emplace(bytes, phase);
+    return phase;
 }
 
 uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg) {
     std::lock_guard<std::mutex> lock(mu_);
     const size_t bytes = round_to_pages(size);
+    const size_t pages = bytes / kSaPageBytes;
     const bool compressed = cfg.compression && comp_ok_;
     if (capacity_ && bytes > capacity_) return 0; // can never fit: do not drain the device trying
+    const int phase = choose_phase(bytes, pages, compressed);
 
-    // 1) exact-size reuse of a block that is still mapped (sideaware.cu:1199-1219)
-    auto hit = cache_.find(cache_key(bytes, compressed));
-    if (hit != cache_.end() && !hit->second.empty()) {
-        Block b = std::move(hit->second.back());
-        hit->second.pop_back();
-        cached_bytes_ -= b.bytes;
-        if (b.stream != stream) {
-            be_->stream_sync(b.stream); // work queued by the previous user must be done
-            b.stream = stream;
-        }
-        b.requested = size;
-        uint64_t base = b.base;
-        live_.emplace(base, std::move(b));
+    // 1) a free run of still-mapped pages (no driver call at all)
+    uint64_t p = take_from_free(pages, phase, compressed, stream);
+    if (p) {
+        live_[p].requested = size;
         st_.reuse_hits++;
         st_.large_allocs++;
-        return base;
+        return p;
     }
-
-    // 2..4) the ladder of sideaware.cu:1233-1252: trim over the threshold, trim everything,
-    // give all pooled pages back to the driver; try to build the block after each step
+    // 2..4) the ladder of sideaware.cu:1233-1252: unmap free memory above the threshold, unmap
+    // all of it, give all pooled pages back to the driver; try to map a new segment after each
     for (int step = 0; step < 3; ++step) {
         if (step == 0) trim_locked(cfg.trim_start, cfg.trim_end);
         else if (step == 1) trim_locked(0, 0);
         else {
             trim_locked(0, 0);
-            for (int c = 0; c < 2; ++c)
-                for (int s = 0; s < 2; ++s) {
-                    for (auto& pg : pool_[c][s]) be_->release_page(pg.handle);
-                    pool_[c][s].clear();
-                }
+            release_pools();
             be_->device_sync();
         }
-        Block b;
-        if (build_block(b, size, compressed, stream, cfg)) {
-            uint64_t base = b.base;
-            live_.emplace(base, std::move(b));
+        p = grow(pages, phase, compressed, stream, cfg);
+        if (p) {
+            live_[p].requested = size;
             st_.large_allocs++;
-            return base;
+            return p;
         }
     }
     // nothing worked: do not sit on the pages gathered while trying
-    for (int c = 0; c < 2; ++c)
-        for (int s = 0; s < 2; ++s) {
-            for (auto& pg : pool_[c][s]) be_->release_page(pg.handle);
-            pool_[c][s].clear();
-        }
+    release_pools();
     return 0;
 }
 
@@ -236,12 +355,16 @@ bool SaAllocator::free(uint64_t ptr, void* stream) {
     std::lock_guard<std::mutex> lock(mu_);
     auto it = live_.find(ptr);
     if (it == live_.end()) return false;
-    Block b = std::move(it->second);
+    Block b = it->second;
     live_.erase(it);
-    (void)stream; // the block remembers the stream it was handed out on (sideaware.cu:1209-1214)
-    b.freed_seq = ++seq_;
-    cached_bytes_ += b.bytes;
-    cache_[cache_key(b.bytes, b.compressed)].push_back(std::move(b));
+    live_bytes_ -= b.pages * kSaPageBytes;
+    (void)stream; // the run remembers the stream the block was handed out on (sideaware.cu:1209-1214)
+    Run run;
+    run.pages = b.pages;
+    run.seg = b.seg;
+    run.freed_seq = ++seq_;
+    run.stream = b.stream;
+    insert_free(ptr, run);
     return true;
 }
 
@@ -260,10 +383,8 @@ size_t SaAllocator::release_unused() {
     trim_locked(0, 0);
     size_t released = 0;
     for (int c = 0; c < 2; ++c)
-        for (int s = 0; s < 2; ++s) {
-            for (auto& pg : pool_[c][s]) { be_->release_page(pg.handle); released += kSaPageBytes; }
-            pool_[c][s].clear();
-        }
+        for (int s = 0; s < 2; ++s) released += pool_[c][s].size() * kSaPageBytes;
+    release_pools();
     be_->device_sync();
     return released;
 }
@@ -271,11 +392,12 @@ size_t SaAllocator::release_unused() {
 SaAllocStats SaAllocator::stats() {
     std::lock_guard<std::mutex> lock(mu_);
     SaAllocStats s = st_;
-    s.bytes_live = 0;
-    for (auto& kv : live_) s.bytes_live += kv.second.bytes;
+    s.bytes_live = live_bytes_;
     s.bytes_cached = cached_bytes_;
     s.pages_pool[0] = pool_[0][0].size() + pool_[1][0].size();
     s.pages_pool[1] = pool_[0][1].size() + pool_[1][1].size();
+    s.segments = segments_.size();
+    s.free_runs = free_.size();
     return s;
 }
 

@@ -409,6 +409,10 @@ SA_API void sideaware_get_stats(sideaware_stats_t* out) {
     out->hash_validation_errors = (unsigned long long)dev->topo.validation_errors;
 }
 
+SA_API void sideaware_driver_call_times(unsigned long long ns_out[8], unsigned long long calls_out[8]) {
+    if (ns_out && calls_out) sa_backend_times(ns_out, calls_out);
+}
+
 SA_API const char* sideaware_topology_json(void) {
     SaDevice* dev = sa_device(-1);
     return dev ? dev->topo.json.c_str() : "{}";

@@ -1,5 +1,6 @@
 #include "sa_context.hpp"
 
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -50,11 +51,29 @@ SaScopedDevice::~SaScopedDevice() {
 // ---------------------------------------------------------------------------
 namespace {
 
+// nanoseconds spent in each kind of backend call (SIDEAWARE_VERBOSE prints them at exit; also in the stats)
+struct BackendTimes {
+    std::atomic<unsigned long long> ns[8];
+    std::atomic<unsigned long long> calls[8];
+};
+BackendTimes g_times;
+enum { T_CREATE, T_RELEASE, T_RESERVE, T_MAP, T_UNMAP, T_ACCESS, T_PROBE, T_SYNC };
+struct ScopedTime {
+    int k;
+    std::chrono::steady_clock::time_point t0;
+    explicit ScopedTime(int kind) : k(kind), t0(std::chrono::steady_clock::now()) {}
+    ~ScopedTime() {
+        g_times.ns[k] += (unsigned long long)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+        g_times.calls[k]++;
+    }
+};
+
 class CudaBackend : public SaBackend {
 public:
     explicit CudaBackend(SaDevice* dev) : dev_(dev), d_(dev->drv) {}
 
     int create_page(uint64_t* handle, bool compressed) override {
+        ScopedTime st(T_CREATE);
         CUmemAllocationProp prop;
         std::memset(&prop, 0, sizeof(prop));
         prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
@@ -66,19 +85,31 @@ public:
         *handle = (uint64_t)h;
         return (int)r;
     }
-    void release_page(uint64_t handle) override { d_->MemRelease((CUmemGenericAllocationHandle)handle); }
+    void release_page(uint64_t handle) override {
+        ScopedTime st(T_RELEASE);
+        d_->MemRelease((CUmemGenericAllocationHandle)handle);
+    }
     int reserve_va(uint64_t* va, size_t bytes) override {
+        ScopedTime st(T_RESERVE);
         CUdeviceptr p = 0;
         CUresult r = d_->MemAddressReserve(&p, bytes, kSaPageBytes, 0, 0);
         *va = (uint64_t)p;
         return (int)r;
     }
-    void free_va(uint64_t va, size_t bytes) override { d_->MemAddressFree((CUdeviceptr)va, bytes); }
+    void free_va(uint64_t va, size_t bytes) override {
+        ScopedTime st(T_RESERVE);
+        d_->MemAddressFree((CUdeviceptr)va, bytes);
+    }
     int map_page(uint64_t va, uint64_t handle) override {
+        ScopedTime st(T_MAP);
         return (int)d_->MemMap((CUdeviceptr)va, kSaPageBytes, 0, (CUmemGenericAllocationHandle)handle, 0);
     }
-    void unmap_page(uint64_t va) override { d_->MemUnmap((CUdeviceptr)va, kSaPageBytes); }
+    void unmap_page(uint64_t va) override {
+        ScopedTime st(T_UNMAP);
+        d_->MemUnmap((CUdeviceptr)va, kSaPageBytes);
+    }
     int set_access(uint64_t va, size_t bytes) override {
+        ScopedTime st(T_ACCESS);
         CUmemAccessDesc acc;
         std::memset(&acc, 0, sizeof(acc));
         acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
@@ -87,6 +118,7 @@ public:
         return (int)d_->MemSetAccess((CUdeviceptr)va, bytes, &acc, 1);
     }
     int probe_pages(uint64_t va, int n, uint8_t* sides, void* /*stream*/) override {
+        ScopedTime st(T_PROBE);
         // fresh pages have no pending work: probe on the library's own stream so the
         // caller's stream is not drained
         std::vector<uint64_t> addrs(n);
@@ -95,8 +127,14 @@ public:
         cudaError_t e = sa_probe_sides(dev_->probe, dev_->topo, addrs.data(), n, sides, dev_->probe_stream, &ambiguous);
         return e == cudaSuccess ? 0 : 1000 + (int)e;
     }
-    void device_sync() override { cudaDeviceSynchronize(); }
-    void stream_sync(void* stream) override { cudaStreamSynchronize((cudaStream_t)stream); }
+    void device_sync() override {
+        ScopedTime st(T_SYNC);
+        cudaDeviceSynchronize();
+    }
+    void stream_sync(void* stream) override {
+        ScopedTime st(T_SYNC);
+        cudaStreamSynchronize((cudaStream_t)stream);
+    }
 
 private:
     SaDevice* dev_;
@@ -278,4 +316,11 @@ SaDevice* sa_device_if_ready(int device) {
     if (device < 0 || device >= (int)g_devices.size() || !g_devices[device]) return nullptr;
     SaDevice* dev = g_devices[device].get();
     return dev->ready ? dev : nullptr;
+}
+
+void sa_backend_times(unsigned long long ns_out[8], unsigned long long calls_out[8]) {
+    for (int i = 0; i < 8; ++i) {
+        ns_out[i] = g_times.ns[i].load();
+        calls_out[i] = g_times.calls[i].load();
+    }
 }

@@ -76,3 +76,6 @@ void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, in
 // The device's state if some earlier call has already set it up, else nullptr.  Never
 // initialises anything (so it never allocates).
 SaDevice* sa_device_if_ready(int device);
+
+// Time spent in driver calls by kind: create, release, reserve/free VA, map, unmap, set access, probe, sync.
+void sa_backend_times(unsigned long long ns_out[8], unsigned long long calls_out[8]);

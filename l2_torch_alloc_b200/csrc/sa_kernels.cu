@@ -63,11 +63,24 @@ __device__ __forceinline__ void rotate(float x, float y, float c, float s, float
     oy = __fadd_rn(__fmul_rn(x, s), __fmul_rn(y, c));
 }
 
+// cos/sin entries that one 16-byte data vector needs: bf16 = 4 pairs (two float4), fp32 = 2 pairs (one)
 template <bool BF16>
-__device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab) {
+struct RopeTab {
+    float4 a, b;
+};
+
+template <bool BF16>
+__device__ __forceinline__ RopeTab<BF16> rope_load_tab(const float4* p) {
+    RopeTab<BF16> t;
+    t.a = __ldg(p);
+    if constexpr (BF16) t.b = __ldg(p + 1);
+    return t;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 rope_apply(uint4 in, const RopeTab<BF16>& t) {
     uint4 out;
     if constexpr (BF16) {
-        // 8 bf16 = 4 pairs, table = 4 x (cos, sin) = two float4, consumed one after the other
         auto pair = [](uint32_t w, float c, float s) {
             float x = __uint_as_float(w << 16), y = __uint_as_float(w & 0xffff0000u);
             float ox, oy;
@@ -75,21 +88,22 @@ __device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab) {
             __nv_bfloat162 b = __floats2bfloat162_rn(ox, oy);
             return *reinterpret_cast<uint32_t*>(&b);
         };
-        const float4 t0 = __ldg(tab);
-        out.x = pair(in.x, t0.x, t0.y);
-        out.y = pair(in.y, t0.z, t0.w);
-        const float4 t1 = __ldg(tab + 1);
-        out.z = pair(in.z, t1.x, t1.y);
-        out.w = pair(in.w, t1.z, t1.w);
+        out.x = pair(in.x, t.a.x, t.a.y);
+        out.y = pair(in.y, t.a.z, t.a.w);
+        out.z = pair(in.z, t.b.x, t.b.y);
+        out.w = pair(in.w, t.b.z, t.b.w);
     } else {
-        // 4 floats = 2 pairs, table = one float4
-        const float4 t = __ldg(tab);
         float ox0, oy0, ox1, oy1;
-        rotate(__uint_as_float(in.x), __uint_as_float(in.y), t.x, t.y, ox0, oy0);
-        rotate(__uint_as_float(in.z), __uint_as_float(in.w), t.z, t.w, ox1, oy1);
+        rotate(__uint_as_float(in.x), __uint_as_float(in.y), t.a.x, t.a.y, ox0, oy0);
+        rotate(__uint_as_float(in.z), __uint_as_float(in.w), t.a.z, t.a.w, ox1, oy1);
         out = make_uint4(__float_as_uint(ox0), __float_as_uint(oy0), __float_as_uint(ox1), __float_as_uint(oy1));
     }
     return out;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab) {
+    return rope_apply<BF16>(in, rope_load_tab<BF16>(tab));
 }
 
 // Position of vector `e` (element index in 16-byte vectors): returns false for a V-head
@@ -135,13 +149,24 @@ sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSide
                 locate(k, r, tok);
                 if (r < sh.rotated_vecs) v[k] = ld_stream(p + k * 32);
             }
+            // When a head is a power-of-two number of vectors that divides the 32-lane stride, every
+            // vector of this lane sits at the same place in its head: the cos/sin entries only change
+            // when the token changes (at most once inside a chunk), so they are fetched once and kept.
+            const bool pos_fixed = sh.head_shift >= 0 && sh.vecs_per_head <= 32u;
+            const uint32_t pos_lane = r0 & (sh.vecs_per_head - 1u);
+            uint32_t have_tok = 0xffffffffu;
+            RopeTab<BF16> tab;
 #pragma unroll
             for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
                 uint32_t r, tok;
                 locate(k, r, tok);
                 if (r < sh.rotated_vecs) {
-                    uint32_t pos = sh.head_shift >= 0 ? (r & (sh.vecs_per_head - 1)) : (r % sh.vecs_per_head);
-                    p[k * 32] = rope_vec<BF16>(v[k], table + tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec);
+                    if (!pos_fixed || tok != have_tok) {
+                        const uint32_t pos = pos_fixed ? pos_lane : (r % sh.vecs_per_head);
+                        tab = rope_load_tab<BF16>(table + tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec);
+                        have_tok = tok;
+                    }
+                    p[k * 32] = rope_apply<BF16>(v[k], tab);
                 }
             }
         } else {

@@ -306,7 +306,7 @@ static void test_alloc() {
         uint64_t s = a.malloc(60 * kSaPageBytes, nullptr, cfg); // unbalanced pool: cross-side pages allowed, still correct
         CHECK(s != 0);
     }
-    {   // threshold trimming: least recently freed blocks go first, down to the end threshold
+    {   // threshold trimming: only when the mapped set must grow; least recently freed runs go first
         FakeDriver d;
         SaAllocator a(&d, false);
         SaAllocConfig c2 = cfg;
@@ -316,12 +316,87 @@ static void test_alloc() {
         for (int i = 0; i < 10; ++i) ps.push_back(a.malloc((size_t)(8 + 2 * i) << 20, nullptr, c2));
         for (uint64_t p : ps) a.free(p, nullptr);
         CHECK(a.stats().bytes_cached == 170ull << 20);
-        uint64_t p = a.malloc(4u << 20, nullptr, c2); // miss -> trim to <= 16 MiB
-        CHECK(p != 0);
+        int syncs_before = d.syncs;
+        uint64_t small = a.malloc(4u << 20, nullptr, c2); // fits into a free run: no driver call, no trim
+        CHECK(small != 0 && a.stats().trims == 0 && d.syncs == syncs_before);
+        CHECK(a.stats().bytes_cached == 166ull << 20);
+        uint64_t big = a.malloc(64u << 20, nullptr, c2);  // no run is large enough -> trim, then map a new segment
+        CHECK(big != 0);
         SaAllocStats st = a.stats();
-        CHECK(st.bytes_cached <= (16u << 20) && st.trims == 1 && d.syncs >= 2);
-        uint64_t again = a.malloc((size_t)(8 + 2 * 9) << 20, nullptr, c2); // most recently freed survived? (26 MiB > 16: no)
-        CHECK(again != 0);
+        CHECK(st.bytes_cached <= (16u << 20) && st.trims == 1 && d.syncs >= syncs_before + 2);
+        CHECK(d.wrong_side_pages(big, 64u << 20) == 0 && d.wrong_side_pages(small, 4u << 20) == 0);
+        a.free(small, nullptr);
+        a.free(big, nullptr);
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+    }
+    {   // runs: split on allocation, merge on free, one skipped page when the run starts on the wrong side
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t seg = a.malloc(64 * kSaPageBytes, nullptr, cfg);
+        CHECK(seg != 0);
+        a.free(seg, nullptr);
+        CHECK(a.stats().free_runs == 1 && a.stats().segments == 1);
+        size_t maps_before = d.mappings.size();
+        uint64_t x = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        uint64_t y = a.malloc(20 * kSaPageBytes, nullptr, cfg);
+        uint64_t z = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        CHECK(x && y && z && d.mappings.size() == maps_before); // all carved out of the mapped segment
+        CHECK(((x >> 21) & 1) == ((z >> 21) & 1));              // same size, same start side
+        for (uint64_t p : {x, y, z}) CHECK(p >= seg && p < seg + 64 * kSaPageBytes);
+        CHECK(d.wrong_side_pages(x, 10 * kSaPageBytes) == 0 && d.wrong_side_pages(y, 20 * kSaPageBytes) == 0);
+        CHECK(!(x < y + 20 * kSaPageBytes && y < x + 10 * kSaPageBytes));
+        a.free(y, nullptr);
+        a.free(x, nullptr);
+        a.free(z, nullptr);
+        SaAllocStats st = a.stats();
+        CHECK(st.free_runs == 1 && st.bytes_cached == 64 * kSaPageBytes && st.bytes_live == 0); // merged back
+        uint64_t again = a.malloc(64 * kSaPageBytes, nullptr, cfg);
+        CHECK(again == seg);
+        a.free(again, nullptr);
+        // an odd-sized block forces the next equal-sized one onto a run that starts on the other side
+        uint64_t o1 = a.malloc(3 * kSaPageBytes, nullptr, cfg);
+        uint64_t o2 = a.malloc(3 * kSaPageBytes, nullptr, cfg);
+        CHECK(o1 && o2 && ((o1 >> 21) & 1) == ((o2 >> 21) & 1));
+        CHECK(d.wrong_side_pages(o1, 3 * kSaPageBytes) == 0 && d.wrong_side_pages(o2, 3 * kSaPageBytes) == 0);
+        CHECK(d.mappings.size() == maps_before);
+    }
+    {   // streams: a run last used on another stream is waited for; merged runs of several streams sync the device
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t p1 = a.malloc(8 * kSaPageBytes, (void*)1, cfg);
+        uint64_t p2 = a.malloc(8 * kSaPageBytes, (void*)2, cfg);
+        a.free(p1, (void*)1);
+        uint64_t q = a.malloc(8 * kSaPageBytes, (void*)1, cfg);
+        CHECK(q == p1 && d.stream_syncs == 0 && d.syncs == 0);
+        a.free(q, (void*)1);
+        q = a.malloc(8 * kSaPageBytes, (void*)3, cfg);
+        CHECK(q == p1 && d.stream_syncs == 1);
+        a.free(q, (void*)3);
+        a.free(p2, (void*)2);
+        (void)p2;
+    }
+    {   // trimming a run in the middle of a segment leaves the rest usable; the range is released with the last page
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t seg = a.malloc(30 * kSaPageBytes, nullptr, cfg);
+        a.free(seg, nullptr);
+        uint64_t x = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        uint64_t y = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        uint64_t z = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        CHECK(x && y && z);
+        a.free(y, nullptr);
+        a.trim(0, 0); // unmaps y's pages only
+        CHECK(a.stats().bytes_cached == 0 && d.mappings.size() == 20 && d.reservations.size() == 1);
+        CHECK(d.wrong_side_pages(x, 10 * kSaPageBytes) == 0 && d.wrong_side_pages(z, 10 * kSaPageBytes) == 0);
+        uint64_t w = a.malloc(10 * kSaPageBytes, nullptr, cfg); // the hole is not reused: a new segment is mapped
+        CHECK(w != 0 && w != y && d.wrong_side_pages(w, 10 * kSaPageBytes) == 0);
+        a.free(x, nullptr);
+        a.free(z, nullptr);
+        a.free(w, nullptr);
+        size_t released = a.release_unused();
+        CHECK(released >= 30 * kSaPageBytes);
+        CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
     }
     {   // skewed physical side distribution still yields correctly placed blocks
         FakeDriver d;
@@ -340,26 +415,49 @@ static void test_alloc() {
         uint64_t q = a.malloc(8u << 20, nullptr, c2);
         CHECK(q != 0 && q != p);
     }
-    {   // long random churn: blocks never overlap, pages are conserved
+    {   // long random churn: blocks never overlap, sit on the right sides, pages are conserved
         FakeDriver d;
         SaAllocator a(&d, false);
+        SaAllocConfig c2 = cfg;
+        c2.trim_start = 512u << 20;
+        c2.trim_end = 64u << 20;
         std::mt19937 rng(3);
         std::vector<std::pair<uint64_t, size_t>> live;
-        for (int i = 0; i < 3000; ++i) {
-            if (live.empty() || (rng() % 3)) {
-                size_t sz = (size_t)(1 + rng() % 64) << 20;
-                uint64_t p = a.malloc(sz, (void*)(uintptr_t)(rng() % 3), cfg);
-                CHECK(p != 0);
-                for (auto& l : live) CHECK(!(p < l.first + l.second && l.first < p + sz));
-                live.push_back({p, sz});
+        std::map<size_t, int> phase_seen;
+        for (int i = 0; i < 4000; ++i) {
+            if (live.empty() || (rng() % 100) < 55) {
+                size_t sz = ((size_t)(1 + rng() % 64) << 20) - (rng() % 3);
+                uint64_t p = a.malloc(sz, (void*)(uintptr_t)(rng() % 3), c2);
+                CHECK(p != 0 && p % kSaPageBytes == 0);
+                size_t bytes = (sz + kSaPageBytes - 1) / kSaPageBytes * kSaPageBytes;
+                for (auto& l : live) CHECK(!(p < l.first + l.second && l.first < p + bytes));
+                if (i % 7 == 0) CHECK(d.wrong_side_pages(p, bytes) == 0);
+                int ph = (int)((p >> 21) & 1);
+                if (phase_seen.count(bytes)) CHECK(phase_seen[bytes] == ph);
+                phase_seen[bytes] = ph;
+                live.push_back({p, bytes});
             } else {
                 size_t k = rng() % live.size();
                 CHECK(a.free(live[k].first, nullptr));
                 live.erase(live.begin() + k);
             }
+            if (i % 500 == 499) {
+                SaAllocStats st = a.stats();
+                size_t live_bytes = 0;
+                for (auto& l : live) live_bytes += l.second;
+                CHECK(st.bytes_live == live_bytes);
+                CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.page_side.size());
+                CHECK(d.mappings.size() == (st.bytes_live + st.bytes_cached) / kSaPageBytes);
+            }
         }
         SaAllocStats st = a.stats();
-        CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.page_side.size());
+        CHECK(st.cross_side_pages == 0);
+        std::printf("alloc churn: %llu allocs, %llu served from mapped runs, %llu pages created, %llu trims, %llu segments, %llu free runs\n",
+                    (unsigned long long)st.large_allocs, (unsigned long long)st.reuse_hits, (unsigned long long)st.pages_created,
+                    (unsigned long long)st.trims, (unsigned long long)st.segments, (unsigned long long)st.free_runs);
+        for (auto& l : live) a.free(l.first, nullptr);
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
     }
     std::printf("alloc: done\n");
 }
