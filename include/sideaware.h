@@ -111,6 +111,14 @@ sideaware_status_t sideaware_rope_forward(void* qkv, const float* freqs_cis,
                                           int B, int T, int Nq, int Nkv, int HS, int dtype,
                                           int device, sideaware_stream_t stream);
 
+/* Backward pass of the same operator, in place on the gradient of the packed tensor:
+ * rotation by the opposite angle, V-head gradients untouched.  Arithmetic of the
+ * reference's apply_rotary_emb_backward / rope_backward_inplace_kernel1
+ * (example_llmc_rope.cu:166-228). */
+sideaware_status_t sideaware_rope_backward(void* dqkv, const float* freqs_cis,
+                                           int B, int T, int Nq, int Nkv, int HS, int dtype,
+                                           int device, sideaware_stream_t stream);
+
 /* out = bf16(a * sigmoid(a) * b * scale), n elements (multiple of 8), the
  * ahead-of-time build of the benchmark's example functor. */
 sideaware_status_t sideaware_silu_mul_bf16(void* out, const void* a, const void* b, float scale,
@@ -158,6 +166,7 @@ typedef struct sideaware_stats_t {
     unsigned long long kernel_launches;
     unsigned long long probe_confidence_ppm; /* min SM signature margin, 1e6 = perfect */
     unsigned long long hash_validation_errors; /* mispredicted validation offsets at init */
+    unsigned long long kernel_wait_timeouts;   /* bounded waits inside kernels that ran out (0 in a healthy run) */
 } sideaware_stats_t;
 void sideaware_get_stats(sideaware_stats_t* out);
 

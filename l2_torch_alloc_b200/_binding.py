@@ -20,7 +20,7 @@ class Stats(ctypes.Structure):
     _fields_ = [(n, c.c_ulonglong) for n in (
         "bytes_mapped_live", "bytes_mapped_cached", "pages_pool_side0", "pages_pool_side1", "pages_created",
         "cross_side_pages", "reuse_hits", "large_allocs", "small_allocs", "trims", "jit_compiles",
-        "kernel_launches", "probe_confidence_ppm", "hash_validation_errors")]
+        "kernel_launches", "probe_confidence_ppm", "hash_validation_errors", "kernel_wait_timeouts")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -59,6 +59,7 @@ SIGNATURES = {
     "sideaware_last_error": (c.c_char_p, []),
     "sideaware_error_count": (c.c_ulonglong, []),
     "sideaware_rope_forward": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "sideaware_rope_backward": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sideaware_silu_mul_bf16": (_i, [_vp, _vp, _vp, c.c_float, _sz, _i, _vp]),
     "sideaware_compile_check": (_i, [c.c_char_p, _i, c.c_char_p, _sz]),
     "sideaware_set_placement": (None, [_i]),

@@ -96,6 +96,11 @@ class SideAware:
         self.lib.sideaware_memcpy(dst, src, num_bytes, device, _stream_ptr(stream))
         self._checked(before, "sideaware_memcpy")
 
+    def rope_backward_ptr(self, dqkv: int, freqs: int, B, T, Nq, Nkv, HS, bf16: bool, device: int = 0, stream=None) -> None:
+        rc = self.lib.sideaware_rope_backward(dqkv, freqs, B, T, Nq, Nkv, HS, 1 if bf16 else 0, device, _stream_ptr(stream))
+        if rc != 0:
+            raise RuntimeError(f"sideaware_rope_backward failed with CUDA error {rc}: {self.last_error()}")
+
     def rope_forward_ptr(self, qkv: int, freqs: int, B, T, Nq, Nkv, HS, bf16: bool, device: int = 0, stream=None) -> None:
         rc = self.lib.sideaware_rope_forward(qkv, freqs, B, T, Nq, Nkv, HS, 1 if bf16 else 0, device, _stream_ptr(stream))
         if rc != 0:
@@ -189,6 +194,16 @@ class SideAware:
         assert tuple(freqs_cis.shape) == (T, HS // 2, 2), "freqs_cis must be [T, HS/2, 2]"
         self.rope_forward_ptr(qkv.data_ptr(), freqs_cis.data_ptr(), B, T, n_q_heads, n_kv_heads, HS,
                               qkv.dtype == torch.bfloat16, qkv.device.index, torch.cuda.current_stream(qkv.device))
+
+    def rope_backward(self, dqkv, freqs_cis, n_q_heads: int, n_kv_heads: int) -> None:
+        """In place on the gradient of a packed [B, T, Nq + 2 Nkv, HS] tensor."""
+        import torch
+        assert dqkv.is_cuda and freqs_cis.is_cuda and dqkv.is_contiguous() and freqs_cis.is_contiguous()
+        assert dqkv.dtype in (torch.float32, torch.bfloat16) and freqs_cis.dtype == torch.float32
+        B, T, H, HS = dqkv.shape
+        assert H == n_q_heads + 2 * n_kv_heads and tuple(freqs_cis.shape) == (T, HS // 2, 2)
+        self.rope_backward_ptr(dqkv.data_ptr(), freqs_cis.data_ptr(), B, T, n_q_heads, n_kv_heads, HS,
+                               dqkv.dtype == torch.bfloat16, dqkv.device.index, torch.cuda.current_stream(dqkv.device))
 
     def silu_mul(self, out, a, b, scale: float) -> None:
         import torch

@@ -174,6 +174,12 @@ SA_API void sideaware_elementwise(int kernel_id, size_t num_bytes,
             sa_set_error("sideaware_memcpy: null pointer");
             return;
         }
+        if (sa_config().memcpy_engine.load() == 1) {
+            sa_prepare_launch(dev, (uint64_t)in0, num_vecs, 0, forced_per_side, false, &s, &grid, &threads, sa_memcpy_bulk_warps());
+            e = sa_launch_memcpy_bulk(s, dev->side_table, grid, out0, in0, (cudaStream_t)stream);
+            if (e != cudaSuccess) sa_set_error("sideaware_memcpy (bulk engine) launch: %s", cudaGetErrorString(e));
+            return;
+        }
         sa_prepare_launch(dev, (uint64_t)in0, num_vecs, parallel_groups, forced_per_side, false, &s, &grid, &threads);
         e = sa_launch_memcpy(s, dev->side_table, grid, threads, out0, in0, (cudaStream_t)stream);
         if (e != cudaSuccess) sa_set_error("sideaware_memcpy launch: %s", cudaGetErrorString(e));
@@ -205,8 +211,21 @@ SA_API void sideaware_memcpy(void* out, const void* in, size_t num_bytes, int de
                           nullptr, 0, 0, 0, device, stream);
 }
 
+static sideaware_status_t rope_launch(void* qkv, const float* freqs_cis, int B, int T, int Nq, int Nkv, int HS, int dtype,
+                                      int device, sideaware_stream_t stream, bool inverse);
+
 SA_API sideaware_status_t sideaware_rope_forward(void* qkv, const float* freqs_cis, int B, int T, int Nq, int Nkv,
                                                  int HS, int dtype, int device, sideaware_stream_t stream) {
+    return rope_launch(qkv, freqs_cis, B, T, Nq, Nkv, HS, dtype, device, stream, false);
+}
+
+SA_API sideaware_status_t sideaware_rope_backward(void* dqkv, const float* freqs_cis, int B, int T, int Nq, int Nkv,
+                                                  int HS, int dtype, int device, sideaware_stream_t stream) {
+    return rope_launch(dqkv, freqs_cis, B, T, Nq, Nkv, HS, dtype, device, stream, true);
+}
+
+static sideaware_status_t rope_launch(void* qkv, const float* freqs_cis, int B, int T, int Nq, int Nkv, int HS, int dtype,
+                                      int device, sideaware_stream_t stream, bool inverse) {
     if (B <= 0 || T <= 0 || Nq < 0 || Nkv < 0 || Nq + Nkv <= 0 || HS <= 0 || (dtype != 0 && dtype != 1) || !qkv || !freqs_cis) {
         sa_set_error("sideaware_rope_forward: invalid argument");
         return cudaErrorInvalidValue;
@@ -229,6 +248,7 @@ SA_API sideaware_status_t sideaware_rope_forward(void* qkv, const float* freqs_c
     sh.tab_vecs_per_token = (uint32_t)HS / 4;
     sh.tab_vecs_per_vec = dtype == 1 ? 2 : 1;
     sh.head_shift = -1;
+    sh.inverse = inverse ? 1 : 0;
     for (int b = 0; b < 31; ++b)
         if ((1u << b) == sh.vecs_per_head) sh.head_shift = b;
     const uint64_t num_vecs = (uint64_t)B * T * sh.vecs_per_row;
@@ -407,6 +427,10 @@ SA_API void sideaware_get_stats(sideaware_stats_t* out) {
     out->kernel_launches = dev->launches.load();
     out->probe_confidence_ppm = (unsigned long long)(dev->topo.confidence > 0 ? dev->topo.confidence * 1e6 : 0);
     out->hash_validation_errors = (unsigned long long)dev->topo.validation_errors;
+    {
+        SaScopedDevice guard(dev->id);
+        out->kernel_wait_timeouts = sa_probe_wait_timeouts(dev->probe);
+    }
 }
 
 SA_API void sideaware_driver_call_times(unsigned long long ns_out[8], unsigned long long calls_out[8]) {

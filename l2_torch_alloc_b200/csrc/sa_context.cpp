@@ -285,7 +285,7 @@ std::vector<SaDevice*> sa_initialised_devices() {
 }
 
 void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
-                       int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads) {
+                       int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads, int exact_warps) {
     std::memset(s, 0, sizeof(*s));
     int groups = parallel_groups > 0 ? parallel_groups : 4;
     if (groups > 4) groups = 4;
@@ -295,7 +295,7 @@ void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, in
         return (v >= 1 && v <= 4) ? v : 0;
     }();
     if (forced_groups && forced_groups < groups) groups = forced_groups; // may only lower a kernel's own choice
-    int warps = groups * 8;
+    int warps = exact_warps > 0 ? exact_warps : groups * 8;
     int g = dev->topo.num_sms;
     if (forced_per_side > 0 && 2 * forced_per_side < g) g = 2 * forced_per_side;
     s->dc_per_ticket = 0;

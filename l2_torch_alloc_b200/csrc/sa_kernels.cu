@@ -69,11 +69,21 @@ struct RopeTab {
     float4 a, b;
 };
 
+// `inverse` flips the sign of the sine entries: x*c - y*(-s) = x*c + y*s and x*(-s) + y*c are,
+// bit for bit, what the reference's backward pass computes (example_llmc_rope.cu:191-192).
 template <bool BF16>
-__device__ __forceinline__ RopeTab<BF16> rope_load_tab(const float4* p) {
+__device__ __forceinline__ RopeTab<BF16> rope_load_tab(const float4* p, bool inverse) {
     RopeTab<BF16> t;
     t.a = __ldg(p);
     if constexpr (BF16) t.b = __ldg(p + 1);
+    if (inverse) {
+        t.a.y = -t.a.y;
+        t.a.w = -t.a.w;
+        if constexpr (BF16) {
+            t.b.y = -t.b.y;
+            t.b.w = -t.b.w;
+        }
+    }
     return t;
 }
 
@@ -102,8 +112,8 @@ __device__ __forceinline__ uint4 rope_apply(uint4 in, const RopeTab<BF16>& t) {
 }
 
 template <bool BF16>
-__device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab) {
-    return rope_apply<BF16>(in, rope_load_tab<BF16>(tab));
+__device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab, bool inverse) {
+    return rope_apply<BF16>(in, rope_load_tab<BF16>(tab, inverse));
 }
 
 // Position of vector `e` (element index in 16-byte vectors): returns false for a V-head
@@ -163,7 +173,7 @@ sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSide
                 if (r < sh.rotated_vecs) {
                     if (!pos_fixed || tok != have_tok) {
                         const uint32_t pos = pos_fixed ? pos_lane : (r % sh.vecs_per_head);
-                        tab = rope_load_tab<BF16>(table + tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec);
+                        tab = rope_load_tab<BF16>(table + tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec, sh.inverse != 0);
                         have_tok = tok;
                     }
                     p[k * 32] = rope_apply<BF16>(v[k], tab);
@@ -176,7 +186,7 @@ sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSide
                 uint32_t ti;
                 if (a >= s.lead && a < s.end && rope_locate(sh, a - s.lead, &ti)) {
                     uint4* p = x + (a - s.lead);
-                    *p = rope_vec<BF16>(ld_stream(p), table + ti);
+                    *p = rope_vec<BF16>(ld_stream(p), table + ti, sh.inverse != 0);
                 }
             }
         }

@@ -14,6 +14,7 @@ struct SaRopeShape {
     uint32_t tab_vecs_per_token; // float4 entries of the cos/sin table per token = HS / 4
     uint32_t tab_vecs_per_vec;   // float4 table entries consumed per data vector (bf16: 2, fp32: 1)
     int32_t head_shift;          // log2(vecs_per_head) if it is a power of two, else -1
+    int32_t inverse;             // 1: rotate by the opposite angle (the backward pass)
 };
 
 cudaError_t sa_launch_memcpy(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* dst, const void* src, cudaStream_t stream);
@@ -24,3 +25,8 @@ cudaError_t sa_launch_silu_mul(const SaSched& s, const SaSideTable& sides, int g
 // Same kernel as sa_launch_memcpy with its ticket counters in a static device array (no allocation).
 cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int device, int grid, int threads, void* dst, const void* src,
                                      cudaStream_t stream);
+// memcpy through bulk asynchronous copies staged in shared memory (sa_memcpy_bulk.cu); the block
+// size is fixed: sa_memcpy_bulk_warps() warps.
+cudaError_t sa_launch_memcpy_bulk(const SaSched& s, const SaSideTable& sides, int grid, void* dst, const void* src,
+                                  cudaStream_t stream);
+int sa_memcpy_bulk_warps();

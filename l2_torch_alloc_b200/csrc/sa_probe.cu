@@ -214,6 +214,17 @@ uint32_t* sa_probe_ticket_slot(SaProbeDevice* p) {
     return p->tickets + (size_t)s * kTicketStride;
 }
 
+unsigned long long sa_probe_wait_timeouts(SaProbeDevice* p) {
+    std::vector<uint32_t> words(kTicketSlots);
+    // word 96 of every slot: a strided copy of one uint32 per slot
+    if (cudaMemcpy2D(words.data(), sizeof(uint32_t), p->tickets + 96, sizeof(uint32_t) * kTicketStride, sizeof(uint32_t),
+                     kTicketSlots, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return 0;
+    unsigned long long total = 0;
+    for (uint32_t w : words) total += w;
+    return total;
+}
+
 cudaError_t sa_probe_sides(SaProbeDevice* p, const SaTopology& topo, const uint64_t* addrs, int n,
                            uint8_t* sides_out, cudaStream_t stream, int* ambiguous_out) {
     std::lock_guard<std::mutex> lock(p->mu);

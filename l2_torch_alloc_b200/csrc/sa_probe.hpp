@@ -43,6 +43,8 @@ cudaError_t sa_probe_sides(SaProbeDevice* p, const SaTopology& topo, const uint6
 // Device pointers owned by the probe object.
 unsigned char* sa_probe_gpu_side_index(SaProbeDevice* p);
 uint32_t* sa_probe_ticket_slot(SaProbeDevice* p); // next free ticket slot (round robin)
+// Sum of the error words of all ticket slots (bounded waits in kernels that ran out); synchronous.
+unsigned long long sa_probe_wait_timeouts(SaProbeDevice* p);
 
 // Pure host analysis of a latency matrix lat[sm][addr] (exposed for CPU tests).
 // offsets[j] is the byte offset of address j inside the probe page; offsets[0] == 0,

@@ -100,13 +100,18 @@ SA_HD void sa_sched_geometry(SaSched& s, sa_u64 addr, sa_u64 num_vecs, sa_u32 wa
     s.lead = (addr & 8191ull) >> 4;
     s.end = s.lead + num_vecs;
     s.num_dc = (s.end + SA_DC_VECS - 1) / SA_DC_VECS;
-    // aim at >= 8 tickets per warp and side, 1..8 double chunks (8..64 KiB) per ticket;
-    // a preset dc_per_ticket is kept (kernels that redo the geometry for another array)
+    // Ticket length.  Short tickets keep the end of the kernel even (the last ticket of a warp is
+    // time the other warps may sit idle), long tickets keep the claim rate down: at full HBM speed
+    // one-double-chunk tickets would mean a same-address atomic every ~6 ns per side.  Aim at >= 24
+    // tickets per warp and side, 1..8 double chunks (8..64 KiB) per ticket, and at least 2 once the
+    // array is large enough for per-warp claims.  A preset dc_per_ticket is kept (kernels that redo
+    // the geometry for another array).
     sa_u64 per = s.dc_per_ticket;
     if (per == 0) {
-        per = warps_per_side ? s.num_dc / ((sa_u64)warps_per_side * 8u) : 1;
+        per = warps_per_side ? s.num_dc / ((sa_u64)warps_per_side * 24u) : 1;
         if (per < 1) per = 1;
         if (per > 8) per = 8;
+        if (per < 2 && warps_per_side && s.num_dc >= 4ull * warps_per_side) per = 2;
     }
     s.dc_per_ticket = (sa_u32)per;
     s.num_tickets = (sa_u32)((s.num_dc + per - 1) / per);

@@ -30,6 +30,9 @@ def register(sa) -> None:
     def rope_forward(qkv: Tensor, freqs_cis: Tensor, n_q_heads: int, n_kv_heads: int) -> None:
         sa.rope_forward(qkv, freqs_cis, n_q_heads, n_kv_heads)
 
+    def rope_backward(dqkv: Tensor, freqs_cis: Tensor, n_q_heads: int, n_kv_heads: int) -> None:
+        sa.rope_backward(dqkv, freqs_cis, n_q_heads, n_kv_heads)
+
     def silu_mul(out: Tensor, a: Tensor, b: Tensor, scale: float) -> None:
         sa.silu_mul(out, a, b, scale)
 
@@ -44,5 +47,6 @@ def register(sa) -> None:
     reg("one_to_one", one_to_one, ["dst"])
     reg("elementwise", elementwise, ["out0", "out1", "out2", "out3", "sideband_tensor"])
     reg("rope_forward", rope_forward, ["qkv"])
+    reg("rope_backward", rope_backward, ["dqkv"])
     reg("silu_mul", silu_mul, ["out"])
     _registered["lib"] = lib

@@ -57,12 +57,15 @@ def lib() -> ctypes.CDLL:
         L.oracle_precompute_freqs_cis.argtypes = [_f32p, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int]
         L.oracle_rope_forward_f32.argtypes = [_f32p, _f32p, _f32p] + [ctypes.c_int] * 5
         L.oracle_rope_forward_bf16.argtypes = [_u16p, _u16p, _f32p] + [ctypes.c_int] * 5
+        L.oracle_rope_backward_f32.argtypes = [_f32p, _f32p, _f32p] + [ctypes.c_int] * 5
+        L.oracle_rope_backward_bf16.argtypes = [_u16p, _u16p, _f32p] + [ctypes.c_int] * 5
         L.oracle_silu_mul_bf16.argtypes = [_u16p, _u16p, _u16p, ctypes.c_float, ctypes.c_size_t]
         L.oracle_memcpy_mt.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
         L.oracle_rope_forward_mt.argtypes = [ctypes.c_void_p, ctypes.c_void_p, _f32p] + [ctypes.c_int] * 7
         L.oracle_bf16_to_f32.argtypes = [_f32p, _u16p, ctypes.c_size_t]
         L.oracle_f32_to_bf16.argtypes = [_u16p, _f32p, ctypes.c_size_t]
         for f in ("oracle_precompute_freqs_cis", "oracle_rope_forward_f32", "oracle_rope_forward_bf16",
+                  "oracle_rope_backward_f32", "oracle_rope_backward_bf16",
                   "oracle_silu_mul_bf16", "oracle_memcpy_mt", "oracle_rope_forward_mt",
                   "oracle_bf16_to_f32", "oracle_f32_to_bf16"):
             getattr(L, f).restype = None
@@ -91,6 +94,9 @@ def ref() -> ctypes.CDLL:
         R.ref_precompute_freqs_cis.restype = None
         R.ref_apply_rotary_emb_forward.argtypes = [_f32p, _f32p, _f32p] + [ctypes.c_int] * 4
         R.ref_apply_rotary_emb_forward.restype = None
+        if hasattr(R, "ref_apply_rotary_emb_backward"):
+            R.ref_apply_rotary_emb_backward.argtypes = [_f32p, _f32p, _f32p, _f32p] + [ctypes.c_int] * 4
+            R.ref_apply_rotary_emb_backward.restype = None
         _REF = R
     return _REF
 
@@ -123,6 +129,23 @@ def rope_forward_bf16(inp_u16: np.ndarray, table: np.ndarray, B, T, Nq, Nkv, HS,
     else:
         lib().oracle_rope_forward_bf16(_ptr(out, _u16p), _ptr(inp_u16, _u16p), _ptr(table, _f32p), B, T, Nq, Nkv, HS)
     return out
+
+
+def rope_backward_f32(dout: np.ndarray, table: np.ndarray, B, T, Nq, Nkv, HS) -> np.ndarray:
+    """Gradient w.r.t. the input, accumulated into zeros as the reference does (example_llmc_rope.cu:166-195)."""
+    dout = np.ascontiguousarray(dout, dtype=np.float32)
+    table = np.ascontiguousarray(table, dtype=np.float32)
+    dinp = np.zeros_like(dout)
+    lib().oracle_rope_backward_f32(_ptr(dinp, _f32p), _ptr(dout, _f32p), _ptr(table, _f32p), B, T, Nq, Nkv, HS)
+    return dinp
+
+
+def rope_backward_bf16(dout_u16: np.ndarray, table: np.ndarray, B, T, Nq, Nkv, HS) -> np.ndarray:
+    dout_u16 = np.ascontiguousarray(dout_u16, dtype=np.uint16)
+    table = np.ascontiguousarray(table, dtype=np.float32)
+    dinp = np.empty_like(dout_u16)
+    lib().oracle_rope_backward_bf16(_ptr(dinp, _u16p), _ptr(dout_u16, _u16p), _ptr(table, _f32p), B, T, Nq, Nkv, HS)
+    return dinp
 
 
 def silu_mul_bf16(a_u16: np.ndarray, b_u16: np.ndarray, scale: float) -> np.ndarray:

@@ -17,3 +17,8 @@ REF_EXPORT void ref_apply_rotary_emb_forward(float* out, const float* inp, const
                                              int B, int T, int n_head, int head_dim) {
     apply_rotary_emb_forward(out, inp, table, B, T, n_head, head_dim);
 }
+
+REF_EXPORT void ref_apply_rotary_emb_backward(float* dinp, const float* dout, const float* inp, const float* table,
+                                              int B, int T, int n_head, int head_dim) {
+    apply_rotary_emb_backward(dinp, dout, inp, table, B, T, n_head, head_dim);
+}

@@ -96,6 +96,36 @@ void oracle_rope_forward_f32(float *out, const float *inp, const float *table,
     }
 }
 
+/* Backward pass (gradient w.r.t. the input).  Follows example_llmc_rope.cu:166-195
+ * (apply_rotary_emb_backward): the rotation by the opposite angle,
+ *     (gx, gy) -> (gx*c + gy*s, -gx*s + gy*c),
+ * ACCUMULATED into dinp (the reference adds to a zero-initialised buffer), V heads copied. */
+void oracle_rope_backward_f32(float *dinp, const float *dout, const float *table,
+                              int B, int T, int Nq, int Nkv, int HS)
+{
+    const int heads = Nq + 2 * Nkv;
+    const int rotated = Nq + Nkv;
+    for (int b = 0; b < B; b++) {
+        for (int t = 0; t < T; t++) {
+            const size_t row = ((size_t)b * T + t) * heads * HS;
+            const float *trow = table + (size_t)t * HS;
+            for (int h = 0; h < heads; h++) {
+                const size_t base = row + (size_t)h * HS;
+                if (h >= rotated) {
+                    memcpy(dinp + base, dout + base, sizeof(float) * HS);
+                    continue;
+                }
+                for (int d = 0; d < HS / 2; d++) {
+                    float gx = dout[base + 2 * d], gy = dout[base + 2 * d + 1];
+                    float c = trow[2 * d], s = trow[2 * d + 1];
+                    dinp[base + 2 * d] += gx * c + gy * s;
+                    dinp[base + 2 * d + 1] += -gx * s + gy * c;
+                }
+            }
+        }
+    }
+}
+
 /* ------------------------------------------------------------------------- */
 /* bfloat16 storage helpers: widening is exact; narrowing is round-to-nearest-
  * even with NaN kept quiet, the conversion CUDA's cvt.rn.bf16.f32 performs. */
@@ -149,6 +179,36 @@ void oracle_rope_forward_bf16(uint16_t *out, const uint16_t *inp, const float *t
                     float c = trow[2 * d], s = trow[2 * d + 1];
                     out[base + 2 * d] = f32_to_bf16_rne(x * c - y * s);
                     out[base + 2 * d + 1] = f32_to_bf16_rne(x * s + y * c);
+                }
+            }
+        }
+    }
+}
+
+/* bf16 storage flavour of the backward pass: widen, rotate by the opposite angle with
+ * separate fp32 roundings, narrow once (no accumulation: the result replaces the gradient,
+ * as the in-place GPU kernel of the reference does, example_llmc_rope.cu:197-228). */
+void oracle_rope_backward_bf16(uint16_t *dinp, const uint16_t *dout, const float *table,
+                               int B, int T, int Nq, int Nkv, int HS)
+{
+    const int heads = Nq + 2 * Nkv;
+    const int rotated = Nq + Nkv;
+    for (int b = 0; b < B; b++) {
+        for (int t = 0; t < T; t++) {
+            const size_t row = ((size_t)b * T + t) * heads * HS;
+            const float *trow = table + (size_t)t * HS;
+            for (int h = 0; h < heads; h++) {
+                const size_t base = row + (size_t)h * HS;
+                if (h >= rotated) {
+                    memcpy(dinp + base, dout + base, sizeof(uint16_t) * HS);
+                    continue;
+                }
+                for (int d = 0; d < HS / 2; d++) {
+                    float gx = bf16_to_f32(dout[base + 2 * d]);
+                    float gy = bf16_to_f32(dout[base + 2 * d + 1]);
+                    float c = trow[2 * d], s = trow[2 * d + 1];
+                    dinp[base + 2 * d] = f32_to_bf16_rne(gx * c + gy * s);
+                    dinp[base + 2 * d + 1] = f32_to_bf16_rne(-gx * s + gy * c);
                 }
             }
         }

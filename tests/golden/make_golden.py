@@ -7,7 +7,8 @@ Run where the reference tree is available (it is compiled in place by
 
 Outputs (all small, committed):
   rope_small_f32.npz   input/table/output of the reference's CPU RoPE on a tiny
-                       packed-QKV tensor, llama-3 scaling off and on
+                       packed-QKV tensor, llama-3 scaling off and on, plus the
+                       reference's backward pass applied to that output
   rope_gqa_bf16.npz    grouped-query bf16 case obtained from the unmodified
                        reference function through the padded-head construction
                        (rotation depends on (t, d) only)
@@ -42,6 +43,14 @@ def ref_forward(inp, table, B, T, NH, HS):
     return out
 
 
+def ref_backward(dout, table, B, T, NH, HS):
+    dout = np.ascontiguousarray(dout, dtype=np.float32)
+    dinp = np.zeros_like(dout)  # the reference accumulates into a zeroed buffer (example_llmc_rope.cu:301-303)
+    oracle.ref().ref_apply_rotary_emb_backward(oracle._ptr(dinp, _f32p), oracle._ptr(dout, _f32p), oracle._ptr(dout, _f32p),
+                                               oracle._ptr(table, _f32p), B, T, NH, HS)
+    return dinp
+
+
 def main():
     assert oracle.ref_available(), "build oracle/_ref first (make -C oracle ref)"
 
@@ -54,6 +63,7 @@ def main():
         tab = ref_table(HS, T, 10000.0, scaled)
         out[f"table_s{scaled}"] = tab
         out[f"out_s{scaled}"] = ref_forward(inp, tab, B, T, NH, HS)
+        out[f"dinp_s{scaled}"] = ref_backward(out[f"out_s{scaled}"], tab, B, T, NH, HS)  # gradient = forward output
     np.savez_compressed(os.path.join(HERE, "rope_small_f32.npz"), inp=inp,
                         shape=np.array([B, T, NH, HS]), **out)
 

@@ -112,3 +112,31 @@ def test_functor_headers_compile_for_sm100a(sa, wide):
 def test_bad_header_reports_the_compiler_log(sa):
     log = sa.compile_check(b"typedef int o0; this is not CUDA;")
     assert "error" in log.lower()
+
+
+def test_cpp_header_instantiates_and_links(tmp_path):
+    """include/sideaware.hpp: the templated conveniences compile and link against the library
+    (the reference's kernel wrappers, sideaware.cu:1549-1570, cannot be instantiated)."""
+    import subprocess
+    src = tmp_path / "use.cpp"
+    src.write_text("""
+#include "sideaware.hpp"
+int main(int argc, char**) {
+    float* p = nullptr;
+    if (argc > 100) {
+        sideaware::malloc(&p, 1024);
+        sideaware::malloc_async(&p, 1024);
+        sideaware::memcpy(p, (const float*)p, 256);
+        sideaware::one_to_one(0, p, (const float*)p, 1024);
+        sideaware::elementwise(0, 1024, p, nullptr, nullptr, nullptr, p);
+        sideaware::free_async(p);
+        sideaware::free(p);
+    }
+    return sideaware_create_kernel("") == 0 ? 0 : 1;
+}
+""")
+    libdir = os.path.join(ROOT, "l2_torch_alloc_b200")
+    exe = tmp_path / "use"
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src),
+                           "-L", libdir, "-l:sideaware.so", f"-Wl,-rpath,{libdir}", "-o", str(exe)])
+    assert subprocess.run([str(exe)]).returncode == 0

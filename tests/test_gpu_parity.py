@@ -44,8 +44,11 @@ def rng_bytes(seed, n):
 @pytest.mark.parametrize("nbytes", [16, 48, 4096, 4112, 8192, 12432, 65536 + 16, (1 << 20) + 4096 + 32,
                                     1000 * 1000 * 2, 1000 * 1000 * 8, 10000 * 1000 * 4, (64 << 20)])
 @pytest.mark.parametrize("placement", PLACEMENTS)
-def test_memcpy_bit_exact(sa, nbytes, placement):
+@pytest.mark.parametrize("engine", [0, 1])
+def test_memcpy_bit_exact(sa, nbytes, placement, engine):
+    """engine 0 = 128-bit vector loads/stores, 1 = bulk copies staged through shared memory"""
     sa.set_placement(placement)
+    sa.lib.sideaware_set_memcpy_engine(engine)
     src_host = rng_bytes(0xB200 + 2, nbytes)
     src = ch.Guarded(sa, nbytes)
     dst = ch.Guarded(sa, nbytes)
@@ -57,6 +60,8 @@ def test_memcpy_bit_exact(sa, nbytes, placement):
     assert np.array_equal(got[:nbytes], src_host)
     assert not got[nbytes:].any(), "bytes past the end of the copy were written"
     assert dst.canaries_intact() and src.canaries_intact()
+    assert sa.stats()["kernel_wait_timeouts"] == 0
+    sa.lib.sideaware_set_memcpy_engine(0)
     src.free()
     dst.free()
 
@@ -108,6 +113,33 @@ def test_memcpy_rejects_misuse_without_touching_memory(sa):
     ch.sync()
     assert not ch.d2h(dst.ptr, 1 << 20).any()
     dst.free()
+
+
+@pytest.mark.parametrize("nbytes", [16, 4096, 4112, 12432, (1 << 20) + 4096 + 32, 10000 * 1000 * 4, (96 << 20) + 8192])
+@pytest.mark.parametrize("placement", ["aware", "wrong"])
+def test_memcpy_bulk_engine_bit_exact(sa, nbytes, placement):
+    """Engine 1: bulk asynchronous copies staged through shared memory; same contract, same bytes."""
+    sa.set_placement(placement)
+    sa.lib.sideaware_set_memcpy_engine(1)
+    try:
+        src_host = rng_bytes(0xB200 + 7, nbytes)
+        src = ch.Guarded(sa, nbytes + 8192)
+        dst = ch.Guarded(sa, nbytes + 8192)
+        for off in (0, 4096 + 16):
+            ch.h2d(src.ptr + off, src_host)
+            ch.memset(dst.ptr, 0, dst.payload_bytes)
+            sa.memcpy_ptr(dst.ptr + off, src.ptr + off, nbytes)
+            ch.sync()
+            got = ch.d2h(dst.ptr, dst.payload_bytes)
+            assert np.array_equal(got[off:off + nbytes], src_host)
+            assert not got[:off].any() and not got[off + nbytes:].any()
+        assert dst.canaries_intact() and src.canaries_intact()
+        assert sa.stats()["kernel_wait_timeouts"] == 0
+        src.free()
+        dst.free()
+    finally:
+        sa.lib.sideaware_set_memcpy_engine(0)
+        sa.set_placement("aware")
 
 
 def test_memcpy_large_round_trip_property(sa):
@@ -213,6 +245,56 @@ def test_rope_matches_reference_golden_vectors(sa, golden_dir):
     B, T, Nq, Nkv, HS = (int(v) for v in g["shape"])
     got = run_rope(sa, g["inp_bf16"], g["table"], B, T, Nq, Nkv, HS, bf16=True)
     assert got.tobytes() == g["out_bf16"].tobytes()
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 32, 32, 128), (2, 160, 32, 8, 128), (3, 33, 5, 2, 32), (2, 50, 6, 3, 48)])
+def test_rope_backward_matches_oracle(sa, shape, golden_dir):
+    """In-place backward pass: equal to the oracle (example_llmc_rope.cu:166-195 restated); values compared
+    as numbers because the reference adds into zeros, which turns -0 into +0."""
+    B, T, Nq, Nkv, HS = shape
+    rng = np.random.default_rng(0xB200 + 6)
+    table = oracle.freqs_cis(HS, T, 10000.0, 1)
+    g = rng.uniform(-1, 1, size=(B, T, Nq + 2 * Nkv, HS)).astype(np.float32)
+    want = oracle.rope_backward_f32(g, table, B, T, Nq, Nkv, HS)
+    nbytes = g.nbytes
+    buf = ch.Guarded(sa, nbytes)
+    tab = ch.cuda_malloc(table.nbytes)
+    ch.h2d(buf.ptr, g)
+    ch.h2d(tab, table)
+    sa.rope_backward_ptr(buf.ptr, tab, B, T, Nq, Nkv, HS, False)
+    ch.sync()
+    got = ch.d2h(buf.ptr, nbytes, np.float32).reshape(g.shape)
+    assert np.array_equal(got, want)
+    # forward then backward is the identity up to rounding
+    ch.h2d(buf.ptr, g)
+    sa.rope_forward_ptr(buf.ptr, tab, B, T, Nq, Nkv, HS, False)
+    sa.rope_backward_ptr(buf.ptr, tab, B, T, Nq, Nkv, HS, False)
+    ch.sync()
+    back = ch.d2h(buf.ptr, nbytes, np.float32).reshape(g.shape)
+    assert np.allclose(back, g, rtol=0, atol=2e-6)
+    # bf16 storage
+    gb = oracle.f32_to_bf16(g)
+    wantb = oracle.rope_backward_bf16(gb, table, B, T, Nq, Nkv, HS)
+    ch.h2d(buf.ptr, gb)
+    sa.rope_backward_ptr(buf.ptr, tab, B, T, Nq, Nkv, HS, True)
+    ch.sync()
+    gotb = ch.d2h(buf.ptr, gb.nbytes, np.uint16).reshape(gb.shape)
+    assert np.array_equal(oracle.bf16_to_f32(gotb), oracle.bf16_to_f32(wantb))
+    assert buf.canaries_intact()
+    buf.free()
+    ch.cuda_free(tab)
+    # the reference's own backward output on its tiny case
+    gold = np.load(os.path.join(golden_dir, "rope_small_f32.npz"))
+    Bg, Tg, NHg, HSg = (int(v) for v in gold["shape"])
+    buf = ch.Guarded(sa, gold["out_s1"].nbytes)
+    tab = ch.cuda_malloc(gold["table_s1"].nbytes)
+    ch.h2d(buf.ptr, gold["out_s1"])
+    ch.h2d(tab, gold["table_s1"])
+    sa.rope_backward_ptr(buf.ptr, tab, Bg, Tg, NHg, NHg, HSg, False)
+    ch.sync()
+    assert np.array_equal(ch.d2h(buf.ptr, gold["out_s1"].nbytes, np.float32).reshape(gold["dinp_s1"].shape), gold["dinp_s1"])
+    buf.free()
+    ch.cuda_free(tab)
 
 
 def test_rope_rejects_bad_shapes(sa):

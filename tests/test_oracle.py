@@ -22,6 +22,11 @@ def test_small_f32_matches_reference_golden(golden_dir):
         assert out.tobytes() == g[f"out_s{scaled}"].tobytes()
         out_np = oracle.np_rope_forward_f32(g["inp"], tab, B, T, NH, NH, HS)
         assert out_np.tobytes() == g[f"out_s{scaled}"].tobytes()
+        # backward pass of the reference (example_llmc_rope.cu:166-195) on the forward output
+        dinp = oracle.rope_backward_f32(out, tab, B, T, NH, NH, HS)
+        assert dinp.tobytes() == g[f"dinp_s{scaled}"].tobytes()
+        # rotating back recovers the input up to rounding
+        assert np.allclose(dinp, g["inp"], rtol=0, atol=1e-6)
 
 
 def test_gqa_bf16_matches_reference_golden(golden_dir):
