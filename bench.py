@@ -44,8 +44,8 @@ FUNCTOR_ELEMS = 1 << 30
 HBM_FALLBACK_GBS = 6650.0
 SPEC_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per 1 GiB launch of sa_memcpy_kernel, from the ncu
-# capture summarised in profiles/sa_memcpy_kernel_1GiB_fabric_by_placement.md
-MEMCPY_DRAM_TRAFFIC_BYTES = 2088437504
+# capture summarised in profiles/sa_memcpy_bulk_kernel_1GiB_fabric_by_placement.md
+MEMCPY_DRAM_TRAFFIC_BYTES = 2085908736
 
 
 def env_int(name, default):
@@ -458,7 +458,8 @@ def run_ours(args, ranks):
     peak, peak_kind = measured_peak()
     avg_launch_ms = statistics.mean(each)
     achieved = gbs(2 * MEMCPY_BYTES, avg_launch_ms)
-    roofline = {"bound": "hbm", "kernel": "sa_memcpy_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    engine = lib.sideaware_get_memcpy_engine()
+    roofline = {"bound": "hbm", "kernel": "sa_memcpy_bulk_kernel" if engine == 1 else "sa_memcpy_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_spec_8000": achieved / SPEC_GBS,
                 "traffic": MEMCPY_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": 2 * MEMCPY_BYTES,
                 "best_launch_ms": min(each), "median_launch_ms": statistics.median(each)}
@@ -490,6 +491,10 @@ def run_ours(args, ranks):
         sub_steps = max(5, min(args.steps, 30))
         # ---- the comparison set for the same 1 GiB copy -------------------------------
         comp = {}
+        lib.sideaware_set_memcpy_engine(0)  # the 128-bit vector engine, for comparison with the default bulk engine
+        ms, ea = time_launches(torch, step, sub_steps, 3, None, per_launch=True)
+        comp["kernel_vector_engine_aware"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
+        lib.sideaware_set_memcpy_engine(1)
         for mode in ("aware", "unaware", "wrong"):
             sa.set_placement(mode)
             ms, ea = time_launches(torch, step, sub_steps, 3, None, per_launch=True)

@@ -136,9 +136,10 @@ int sideaware_compile_check(const char* header, int wide, char* log_out, size_t 
  * (sideaware.cu:70-75). */
 void sideaware_set_placement(int mode);
 int sideaware_get_placement(void);
-/* memcpy engine: 0 = 128-bit vector loads/stores, 1 = bulk-copy (TMA) staging
- * through shared memory. */
+/* memcpy engine: 1 (default) = bulk asynchronous copies (TMA unit) staged through
+ * shared memory, 4 KiB per copy; 0 = 128-bit vector loads/stores.  Same results. */
 void sideaware_set_memcpy_engine(int engine);
+int sideaware_get_memcpy_engine(void);
 
 /* Per-chunk side map: writes one byte (0/1) per 4 KiB chunk of
  * [ptr, ptr + num_bytes) to host memory, as predicted from the address hash

@@ -340,7 +340,8 @@ SA_API void sideaware_set_placement(int mode) {
     sa_config().placement.store(mode);
 }
 SA_API int sideaware_get_placement(void) { return sa_config().placement.load(); }
-SA_API void sideaware_set_memcpy_engine(int engine) { sa_config().memcpy_engine.store(engine == 1 ? 1 : 0); }
+SA_API void sideaware_set_memcpy_engine(int engine) { sa_config().memcpy_engine.store(engine == 0 ? 0 : 1); }
+SA_API int sideaware_get_memcpy_engine(void) { return sa_config().memcpy_engine.load(); }
 
 // ---------------------------------------------------------------------------
 // queries

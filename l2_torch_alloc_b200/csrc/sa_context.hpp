@@ -20,7 +20,7 @@ struct SaConfig {
     size_t threshold = 8ull << 20; // sizes below go to cudaMallocAsync in the *_auto entry points
     std::string log_file;          // JIT log destination ("" = none)
     std::atomic<int> placement{0};
-    std::atomic<int> memcpy_engine{0};
+    std::atomic<int> memcpy_engine{1}; // 0 = vector loads/stores, 1 = bulk copies through shared memory
 };
 SaConfig& sa_config();
 

@@ -23,7 +23,7 @@ def main():
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--reps", type=int, default=4)
     ap.add_argument("--placement", default="aware", choices=["aware", "unaware", "wrong"])
-    ap.add_argument("--engine", type=int, default=0)
+    ap.add_argument("--engine", type=int, default=1, help="memcpy engine: 1 = bulk copies (default), 0 = vector")
     args = ap.parse_args()
     sa = pkg.SideAware()
     sa.set_placement(args.placement)

@@ -61,7 +61,7 @@ def test_memcpy_bit_exact(sa, nbytes, placement, engine):
     assert not got[nbytes:].any(), "bytes past the end of the copy were written"
     assert dst.canaries_intact() and src.canaries_intact()
     assert sa.stats()["kernel_wait_timeouts"] == 0
-    sa.lib.sideaware_set_memcpy_engine(0)
+    sa.lib.sideaware_set_memcpy_engine(1)
     src.free()
     dst.free()
 
@@ -138,7 +138,7 @@ def test_memcpy_bulk_engine_bit_exact(sa, nbytes, placement):
         src.free()
         dst.free()
     finally:
-        sa.lib.sideaware_set_memcpy_engine(0)
+        sa.lib.sideaware_set_memcpy_engine(1)
         sa.set_placement("aware")
 
 
