@@ -43,7 +43,7 @@ ROPE_SHAPE = dict(B=8, T=8192, Nq=32, Nkv=8, HS=128)  # Llama-3-8B heads, bf16, 
 FUNCTOR_ELEMS = 1 << 30
 HBM_FALLBACK_GBS = 6650.0
 SPEC_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per 1 GiB launch of sa_memcpy_kernel, from the ncu
+# dram__bytes_read.sum + dram__bytes_write.sum per 1 GiB launch of sa_memcpy_bulk_kernel, from the ncu
 # capture summarised in profiles/sa_memcpy_bulk_kernel_1GiB_fabric_by_placement.md
 MEMCPY_DRAM_TRAFFIC_BYTES = 2085908736
 

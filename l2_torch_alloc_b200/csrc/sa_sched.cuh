@@ -3,12 +3,13 @@
 // Data is cut into 8 KiB "double chunks" anchored at absolute 8 KiB address
 // boundaries of the side-tracking array; the two 4 KiB halves of a double chunk
 // always lie on opposite L2 sides (address bit 12 is part of the side hash).
-// For each side there is a ticket counter in global memory; a warp running on
-// an SM of side s repeatedly claims a ticket (a run of consecutive double
-// chunks) from counter s and processes the halves homed on side s.  When its
-// own side is drained it claims from the other counter, so every half is
-// processed exactly once whatever the placement of thread blocks on SMs.
-// Speed depends on the side table, correctness never does.
+// For each side there is a ticket counter in global memory; a ticket is a run of
+// consecutive double chunks, and whoever holds ticket t of side s processes, of each
+// of its double chunks, the half homed on side s.  Blocks take tickets of their own
+// SM's side first and sweep up the other side's leftovers at the end, so every half
+// is processed exactly once whatever the placement of thread blocks on SMs.
+// Speed depends on the side table, correctness never does.  How tickets are handed
+// out with few atomics is described at sa_for_each_chunk.
 //
 // The reference assigns work statically from a per-SM ordinal and requires one
 // resident block per SM (sideaware.cu:205-213, 264-272, 286-305); its opt-in
