@@ -1,0 +1,141 @@
+"""The optional knobs of the functor-header contract (sideaware.cu:60-109, :170-184) on a B200:
+UNROLLED, LAUNCH_BOUNDS with fewer groups, FORCE_WRONG_SIDE / FORCE_RANDOM_SIDE, DISCARD_INPUTS,
+CUSTOM_VECTOR_OP with sideband memory, CUSTOM_IDX_FUNC with skipping.  Integer / exactly
+representable data, so every comparison is exact."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+BASE = """
+typedef int o0;
+typedef int i0;
+struct unused {};
+typedef unused o1, o2, o3, i1, i2, i3;
+constexpr bool reverse_order = %s;
+constexpr bool input_evict[4] = {1, 0, 0, 0};
+__device__ void elementwise_op(size_t idx, int sideband, o0 &out0, o1 &out1, o2 &out2, o3 &out3,
+                               const i0 &in0, const i1 &in1, const i2 &in2, const i3 &in3) {
+    out0 = in0 * 3 + sideband + (int)(idx & 7);
+}
+"""
+
+
+@pytest.fixture(scope="module")
+def sa():
+    import torch
+    assert torch.cuda.is_available()
+    import l2_torch_alloc_b200 as pkg
+    return pkg.SideAware()
+
+
+def expected(src, sideband):
+    import torch
+    idx = torch.arange(src.numel(), device=src.device, dtype=torch.int64)
+    return (src.to(torch.int64) * 3 + sideband + (idx & 7)).to(torch.int32)
+
+
+@pytest.mark.parametrize("extra,groups", [
+    ("", 0),
+    ("#define UNROLLED 1\n", 0),
+    ("#define UNROLLED 2\n", 0),
+    ("#define UNROLLED 8\n#define LAUNCH_BOUNDS __launch_bounds__(512, 1)\n", 2),
+    ("#define FORCE_WRONG_SIDE true\n", 0),
+    ("#define FORCE_RANDOM_SIDE true\n", 0),
+    ("#define DYNAMIC_INDEX_FOR_CONCURRENT_KERNELS\n", 1),
+    ("#define DISCARD_INPUTS\nconstexpr bool input_discard[4] = {1, 0, 0, 0};\n", 0),
+])
+@pytest.mark.parametrize("reverse", ["false", "true"])
+def test_knobs_keep_results_exact(sa, extra, groups, reverse):
+    import torch
+    n = 3 * 1000 * 1000 + 12  # ragged: not a multiple of a chunk
+    src = torch.randint(-1000, 1000, (n,), dtype=torch.int32, device="cuda")
+    want = expected(src, 5)
+    kid = sa.create_kernel(extra + BASE % reverse)
+    for big in (False, True):  # torch memory below the allocator threshold, then a side-aware block
+        if big:
+            n2 = 24 * 1024 * 1024
+            src = torch.randint(-1000, 1000, (n2,), dtype=torch.int32, device="cuda")
+            want = expected(src, 5)
+        dst = torch.zeros_like(src)
+        sa.elementwise(kid, dst, None, None, None, src, None, None, None, None, 5, groups, 0)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, want)
+
+
+VECTOR_OP = """
+typedef float o0;
+typedef float i0;
+struct unused {};
+typedef unused o1, o2, o3, i1, i2, i3;
+constexpr bool reverse_order = false;
+constexpr bool input_evict[4] = {1, 0, 0, 0};
+#define CUSTOM_VECTOR_OP
+// one scale per 16-byte vector (the micro-scaling pattern the contract mentions, sideaware.cu:81-83):
+// out = in / absmax(vector), absmax written to the sideband array
+__device__ void vector_op(size_type vec_idx, int n, o0 *out0, o1 *out1, o2 *out2, o3 *out3,
+                          const i0 *in0, const i1 *in1, const i2 *in2, const i3 *in3, int *mem, int val) {
+    float m = 0.0f;
+    for (int e = 0; e < n; e++) m = fmaxf(m, fabsf(in0[e]));
+    ((float*)mem)[vec_idx] = m;
+    float scale = m > 0.0f ? __fdiv_rn(1.0f, m) : 0.0f;
+    for (int e = 0; e < n; e++) out0[e] = __fmul_rn(in0[e], scale) + (float)val;
+}
+"""
+
+
+def test_custom_vector_op_with_sideband_memory(sa):
+    import torch
+    n = 4 * (1 << 20) + 4 * 37
+    # powers of two: absmax, reciprocal and products are exact
+    exps = torch.randint(-8, 8, (n,), device="cuda")
+    signs = torch.randint(0, 2, (n,), device="cuda") * 2 - 1
+    x = (signs * torch.pow(2.0, exps.float())).float()
+    out = torch.zeros_like(x)
+    scales = torch.zeros(n // 4, dtype=torch.float32, device="cuda")
+    kid = sa.create_kernel(VECTOR_OP)
+    sa.elementwise(kid, out, None, None, None, x, None, None, None, scales.view(torch.int32), 2)
+    torch.cuda.synchronize()
+    m = x.view(-1, 4).abs().amax(dim=1)
+    assert torch.equal(scales, m)
+    assert torch.equal(out, (x.view(-1, 4) / m[:, None]).reshape(-1) + 2.0)
+
+
+GATHER = """
+typedef float o0;
+typedef float i0;
+typedef float i1;
+struct unused {};
+typedef unused o1, o2, o3, i2, i3;
+constexpr bool reverse_order = false;
+constexpr bool input_evict[4] = {1, 0, 0, 0};
+__device__ void elementwise_op(size_t idx, int sideband, o0 &out0, o1 &out1, o2 &out2, o3 &out3,
+                               const i0 &in0, const i1 &in1, const i2 &in2, const i3 &in3) {
+    out0 = in0 + in1;
+}
+#define CUSTOM_IDX_FUNC
+// in1 is a short row broadcast over the long array; every 5th row of 64 vectors is left untouched
+__device__ bool indexing(size_type vec_idx, int n, size_type &idx_i0, size_type &idx_i1,
+                         size_type &idx_i2, size_type &idx_i3, int *mem, int val) {
+    idx_i0 = vec_idx;
+    idx_i1 = vec_idx % val;
+    return ((vec_idx / 64) % 5) == 4;
+}
+"""
+
+
+def test_custom_index_function_broadcast_and_skip(sa):
+    import torch
+    rows, row_vecs, bias_vecs = 6000, 64, 48
+    n = rows * row_vecs * 4
+    x = torch.arange(n, dtype=torch.float32, device="cuda") % 1024
+    bias = torch.arange(bias_vecs * 4, dtype=torch.float32, device="cuda") * 4
+    out = x.clone()
+    kid = sa.create_kernel(GATHER)
+    sa.elementwise(kid, out, None, None, None, x, bias, None, None, None, bias_vecs)
+    torch.cuda.synchronize()
+    vec = torch.arange(n // 4, device="cuda")
+    want = x.view(-1, 4) + bias.view(-1, 4)[vec % bias_vecs]
+    keep = ((vec // 64) % 5) == 4
+    want[keep] = x.view(-1, 4)[keep]
+    assert torch.equal(out.view(-1, 4), want)
