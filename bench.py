@@ -651,7 +651,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--churn-ops", type=int, default=10000, help="allocator churn operations (N = 1 only; 0 = skip)")
+    ap.add_argument("--churn-ops", type=int, default=5000,
+                    help="allocator churn operations (N = 1 only; 0 = skip; the full configuration is 10000)")
     ap.add_argument("--power-seconds", type=float, default=2.0, help="length of each power sampling loop (0 = skip)")
     ap.add_argument("--check-ranks", action="store_true",
                     help="exercise only the rank plumbing (barrier, max/sum over ranks, rank 0 prints); needs no GPU")
