@@ -3,6 +3,7 @@
 #include <dlfcn.h>
 #include <unistd.h>
 
+#include <cctype>
 #include <cstdio>
 #include <cstdlib>
 #include <ctime>
@@ -115,8 +116,9 @@ int sa_jit_default_groups(int id) {
 
 // The translation unit for one functor: the four definitions the reference prepends
 // (sideaware.cu:786-795), the user's header, the scheduler and the kernel template.
-static std::string build_source(const std::string& header, int num_sms, uint32_t hash, bool wide) {
+static std::string build_source(const std::string& header, int num_sms, uint32_t hash, bool wide, bool batch_as_written) {
     std::string src;
+    if (batch_as_written) src += "#define SA_BATCH_AS_WRITTEN 1\n";
     src += "#define MAX_SM " + std::to_string(num_sms) + "\n";
     src += "#define HASH " + std::to_string((hash | (1u << 21)) / 16u) + "\n";
     src += wide ? "using size_type = long long;\nconstexpr bool aligned_2MiB = false;\n"
@@ -131,11 +133,13 @@ static std::string build_source(const std::string& header, int num_sms, uint32_t
 }
 
 // NVRTC for sm_100a only.  Returns false and fills *why (with the compiler log) on failure.
-static bool nvrtc_compile(const std::string& src, int id, bool wide, std::vector<char>* cubin, std::string* why) {
+static bool nvrtc_compile(const std::string& src, int id, bool wide, std::vector<char>* cubin, std::string* why,
+                          long* spill_bytes = nullptr) {
     std::call_once(g_nvrtc_once, load_nvrtc);
     if (!g_nvrtc_ok) { *why = g_nvrtc_why; return false; }
     std::string inc = "-I" + cuda_include_dir();
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--generate-line-info", "-use_fast_math", "-std=c++17", inc.c_str()};
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--generate-line-info", "-use_fast_math", "-std=c++17",
+                          "--ptxas-options=-v", inc.c_str()};
     nvrtcProgram prog = nullptr;
     int rc = g_nvrtc.CreateProgram(&prog, src.c_str(), "side_aware.cu", 0, nullptr, nullptr);
     if (rc != 0) { *why = std::string("nvrtcCreateProgram: ") + g_nvrtc.GetErrorString(rc); return false; }
@@ -161,6 +165,16 @@ static bool nvrtc_compile(const std::string& src, int id, bool wide, std::vector
             std::fclose(f);
         }
     }
+    if (spill_bytes) { // "... N bytes spill stores, M bytes spill loads" in the ptxas part of the log
+        *spill_bytes = 0;
+        size_t pos = 0;
+        while ((pos = log.find(" bytes spill stores", pos)) != std::string::npos) {
+            size_t b = pos;
+            while (b > 0 && std::isdigit((unsigned char)log[b - 1])) --b;
+            *spill_bytes += std::atol(log.substr(b, pos - b).c_str());
+            pos += 10;
+        }
+    }
     if (rc != 0) {
         *why = std::string("NVRTC compilation failed (") + g_nvrtc.GetErrorString(rc) + "):\n" + log;
         g_nvrtc.DestroyProgram(&prog);
@@ -178,7 +192,7 @@ static bool nvrtc_compile(const std::string& src, int id, bool wide, std::vector
 
 bool sa_jit_compile_only(const char* header, bool wide, std::string* why) {
     std::vector<char> cubin;
-    return nvrtc_compile(build_source(header ? header : "", 148, 0x1EF000u, wide), -1, wide, &cubin, why);
+    return nvrtc_compile(build_source(header ? header : "", 148, 0x1EF000u, wide, false), -1, wide, &cubin, why);
 }
 
 static bool compile_variant(SaDevice* dev, int id, bool wide, CUfunction* fn_out, CUmodule* mod_out, std::string* why) {
@@ -188,7 +202,17 @@ static bool compile_variant(SaDevice* dev, int id, bool wide, CUfunction* fn_out
         header = g_headers[id].text;
     }
     std::vector<char> cubin;
-    if (!nvrtc_compile(build_source(header, dev->topo.num_sms, dev->topo.hash, wide), id, wide, &cubin, why)) return false;
+    long spills = 0;
+    if (!nvrtc_compile(build_source(header, dev->topo.num_sms, dev->topo.hash, wide, false), id, wide, &cubin, why, &spills)) return false;
+    if (spills > 0) {
+        // the widened batch does not fit the register budget of this functor: use the batch the header asks for
+        std::vector<char> narrow;
+        std::string why2;
+        long spills2 = 0;
+        if (nvrtc_compile(build_source(header, dev->topo.num_sms, dev->topo.hash, wide, true), id, wide, &narrow, &why2, &spills2) &&
+            spills2 < spills)
+            cubin.swap(narrow);
+    }
     CUresult r = dev->drv->ModuleLoadData(mod_out, cubin.data());
     if (r != CUDA_SUCCESS) { *why = "cuModuleLoadData: " + sa_cu_error(dev->drv, r); return false; }
     r = dev->drv->ModuleGetFunction(fn_out, *mod_out, "sideaware_elementwise");

@@ -19,7 +19,7 @@
 // The widest array (i0, or o0 if its element is larger) is moved as 16-byte
 // vectors; the others move vec_size elements per vector with 16/8/4/2/1-byte
 // accesses.  A warp owns one 4 KiB chunk of the widest array at a time and
-// processes it in batches of UNROLLED vectors per lane: all loads of a batch
+// processes it in batches of vectors per lane (sa_batch below): all loads of a batch
 // are issued before its arithmetic and stores.
 
 #ifndef UNROLLED
@@ -38,7 +38,6 @@ constexpr bool input_discard[4] = {false, false, false, false};
 #define FORCE_RANDOM_SIDE false
 #endif
 
-constexpr int sa_batch = (UNROLLED) >= 8 ? 8 : (UNROLLED) >= 4 ? 4 : (UNROLLED) >= 2 ? 2 : 1;
 constexpr bool sideaware_for_o0 = sizeof(o0) > sizeof(i0);
 constexpr int vec_size = 16 / (int)(sideaware_for_o0 ? sizeof(o0) : sizeof(i0));
 
@@ -51,6 +50,21 @@ template <typename T, int BYTES = (int)sizeof(T) * vec_size>
 struct alignas(BYTES == 16 || BYTES == 8 || BYTES == 4 || BYTES == 2 ? BYTES : alignof(T)) sa_pack {
     T v[vec_size];
 };
+
+// Vectors each lane keeps in flight (loads issued before the arithmetic of the batch starts).
+// UNROLLED is the header author's wish; on top of that the batch is widened while the inputs of
+// a batch fit in about 32 registers, because bytes in flight are what hides HBM latency.  The
+// library compiles this version first and falls back to the batch as written
+// (SA_BATCH_AS_WRITTEN) if the compiler had to spill registers.
+constexpr int sa_user_batch = (UNROLLED) >= 8 ? 8 : (UNROLLED) >= 4 ? 4 : (UNROLLED) >= 2 ? 2 : 1;
+constexpr int sa_in_bytes = (sa_used<i0> ? (int)sizeof(sa_pack<i0>) : 0) + (sa_used<i1> ? (int)sizeof(sa_pack<i1>) : 0) +
+                            (sa_used<i2> ? (int)sizeof(sa_pack<i2>) : 0) + (sa_used<i3> ? (int)sizeof(sa_pack<i3>) : 0);
+constexpr int sa_auto_batch = sa_in_bytes <= 16 ? 8 : sa_in_bytes <= 32 ? 4 : sa_in_bytes <= 64 ? 2 : 1;
+#ifdef SA_BATCH_AS_WRITTEN
+constexpr int sa_batch = sa_user_batch;
+#else
+constexpr int sa_batch = sa_auto_batch > sa_user_batch ? sa_auto_batch : sa_user_batch;
+#endif
 
 #ifndef CUSTOM_VECTOR_OP
 __device__ __forceinline__ void vector_op(size_type vec_idx, int n,

@@ -36,3 +36,20 @@ def test_memcpy_not_slower_than_the_reference_kernel():
         assert ref["sizes"][n]["exact"] and ours["sizes"][n]["exact"]
     one_gib = str(1 << 30)
     assert ours["sizes"][one_gib]["gbs"] >= 0.97 * ref["sizes"][one_gib]["gbs"]
+
+
+@pytest.mark.skipif(not os.path.exists(REF), reason="compiled reference not present")
+def test_rope_functor_not_slower_than_the_reference_template():
+    """The same fp32 RoPE functor header through both libraries' NVRTC paths (the reference's kernel
+    template vs this library's), at the reference example's shape, each checked against the oracle."""
+    out = {}
+    for name, lib in (("reference", REF), ("ours", OURS)):
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "rope_functor_timing_script.py"), lib],
+                           capture_output=True, text=True, timeout=600, cwd=ROOT)
+        lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+        assert lines, r.stdout[-2000:] + r.stderr[-2000:]
+        out[name] = json.loads(lines[-1][7:])
+        print(name, json.dumps(out[name]))
+    assert out["ours"]["bit_exact"], "this library's functor path must reproduce the oracle bit for bit"
+    assert out["reference"]["within_1e-6"], "the reference's fast-math JIT stays within its own tolerance"
+    assert out["ours"]["gbs"] >= 0.90 * out["reference"]["gbs"]  # separate processes, short kernel: allow run-to-run noise
