@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdlib>
 
 #include "sa_kernels.hpp"
@@ -29,11 +30,24 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 
-__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+// hinted = true: the line is marked evict-first in L2 (streamed data is not read again)
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar, bool hinted,
+                                          uint64_t policy) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
+    if (hinted)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                     ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+                     : "memory");
+    else
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+                     : "memory");
 }
 
 // true when the phase with the given parity has completed
@@ -52,8 +66,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes, bool hinted, uint64_t policy) {
+    if (hinted)
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
+                     ::"l"(dst), "r"(src_smem), "r"(bytes), "l"(policy)
+                     : "memory");
+    else
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
@@ -67,7 +86,9 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 template <int WARPS, int S>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 sa_memcpy_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSideTable sides,
-                      uint4* __restrict__ dst, const uint4* __restrict__ src) {
+                      uint4* __restrict__ dst, const uint4* __restrict__ src, int hints) {
+    const uint64_t policy = l2_evict_first_policy();
+    const bool hint_load = hints & 1, hint_store = hints & 2;
     constexpr uint32_t L = S >= 3 ? S - 2 : 1;
     extern __shared__ __align__(128) unsigned char stage_mem[]; // [warps][stages][4 KiB]
     __shared__ __align__(8) unsigned long long bars[WARPS * S];
@@ -89,7 +110,7 @@ sa_memcpy_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__
     auto retire = [&]() { // wait for the oldest chunk in flight and send it out
         const uint32_t st = retired % S;
         if (mbar_wait(my_bar0 + 8u * st, (phase_bits >> st) & 1u)) {
-            bulk_store(my_dsts[st], my_stage0 + st * kChunkBytes, kChunkBytes);
+            bulk_store(my_dsts[st], my_stage0 + st * kChunkBytes, kChunkBytes, hint_store, policy);
         } else {
             atomicAdd(s.tickets + 96, 1u); // reported by the host; the copy is incomplete
         }
@@ -104,7 +125,7 @@ sa_memcpy_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__
                 const uint32_t st = issued % S;
                 // the store that last used this stage (S chunks ago) must have read it
                 bulk_wait_read<(S >= 3 ? 1 : 0)>();
-                bulk_load(my_stage0 + st * kChunkBytes, src + e, kChunkBytes, my_bar0 + 8u * st);
+                bulk_load(my_stage0 + st * kChunkBytes, src + e, kChunkBytes, my_bar0 + 8u * st, hint_load, policy);
                 my_dsts[st] = dst + e;
                 ++issued;
                 while (issued - retired > L) retire(); // older chunks go out while newer ones come in
@@ -127,10 +148,20 @@ sa_memcpy_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__
 template <int WARPS, int S>
 cudaError_t launch_cfg(const SaSched& s, const SaSideTable& sides, int grid, void* dst, const void* src, cudaStream_t stream) {
     constexpr int smem = WARPS * S * (int)kChunkBytes;
-    // per device (the attribute belongs to the current device's copy of the function); cheap
-    cudaError_t attr = cudaFuncSetAttribute(sa_memcpy_bulk_kernel<WARPS, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (attr != cudaSuccess) return attr;
-    sa_memcpy_bulk_kernel<WARPS, S><<<grid, WARPS * 32, smem, stream>>>(s, sides, (uint4*)dst, (const uint4*)src);
+    // once per device: the attribute belongs to the current device's copy of the function
+    static std::atomic<bool> opted_in[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !opted_in[dev].load(std::memory_order_acquire)) {
+        cudaError_t attr = cudaFuncSetAttribute(sa_memcpy_bulk_kernel<WARPS, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (attr != cudaSuccess) return attr;
+        if (dev >= 0 && dev < 64) opted_in[dev].store(true, std::memory_order_release);
+    }
+    static const int hints = [] { // tuning aid: SIDEAWARE_BULK_HINTS bit 0 = evict-first loads, bit 1 = evict-first stores
+        const char* e = std::getenv("SIDEAWARE_BULK_HINTS");
+        return e ? std::atoi(e) & 3 : 0;
+    }();
+    sa_memcpy_bulk_kernel<WARPS, S><<<grid, WARPS * 32, smem, stream>>>(s, sides, (uint4*)dst, (const uint4*)src, hints);
     return cudaGetLastError();
 }
 
