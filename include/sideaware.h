@@ -73,7 +73,7 @@ int sideaware_create_kernel(const char* header);
 /* ---- configuration (replaces sideaware.cu:1467-1487) ---------------------- */
 void sideaware_compression(bool enable);
 void sideaware_alloc_threshold(size_t threshold);
-void sideaware_prealloc_config(int extra_required, int extra_alloc);
+void sideaware_prealloc_config(int extra_required, int extra_alloc); /* accepted; pages are created on demand here */
 void sideaware_free_mapped_thresholds(size_t start_threshold, size_t end_threshold);
 /* The reference appends a disassembly of each JIT-ed kernel to this file; this
  * library appends the NVRTC log and the generated source instead. */

@@ -19,81 +19,6 @@ SaAllocator::~SaAllocator() {
 // physical pages
 // ---------------------------------------------------------------------------
 
-// Creates `count` physical pages, learns their side through a temporary mapping and
-// files them in the pools.  Partial success is success (as sideaware.cu:1029-1033).
-int SaAllocator::create_pages(int count, bool compressed, void* stream, const SaAllocConfig& cfg, int* created) {
-    int last_error = 0;
-    *created = 0;
-    const int batch_cap = std::max(1, cfg.max_probe_batch);
-    std::vector<uint8_t> sides;
-    while (count > 0) {
-        int batch = std::min(count, batch_cap);
-        uint64_t va = 0;
-        last_error = be_->reserve_va(&va, (size_t)batch * kSaPageBytes);
-        if (last_error) break;
-        std::vector<uint64_t> handles;
-        handles.reserve(batch);
-        for (int i = 0; i < batch; ++i) {
-            uint64_t h = 0;
-            last_error = be_->create_page(&h, compressed);
-            if (last_error) break;
-            last_error = be_->map_page(va + (uint64_t)i * kSaPageBytes, h);
-            if (last_error) { be_->release_page(h); break; }
-            handles.push_back(h);
-        }
-        int got = (int)handles.size();
-        bool ok = got > 0;
-        if (ok) {
-            last_error = be_->set_access(va, (size_t)got * kSaPageBytes);
-            ok = last_error == 0;
-        }
-        if (ok) {
-            sides.assign(got, 0);
-            last_error = be_->probe_pages(va, got, sides.data(), stream);
-            ok = last_error == 0;
-        }
-        for (int i = 0; i < got; ++i) be_->unmap_page(va + (uint64_t)i * kSaPageBytes);
-        be_->free_va(va, (size_t)batch * kSaPageBytes);
-        if (!ok) {
-            for (uint64_t h : handles) be_->release_page(h);
-            break;
-        }
-        for (int i = 0; i < got; ++i) {
-            pool_[compressed][sides[i] & 1].push_back(Page{handles[i], (uint8_t)(sides[i] & 1)});
-            seen_side_[sides[i] & 1]++;
-        }
-        st_.pages_created += got;
-        *created += got;
-        count -= got;
-        if (got < batch) break; // device memory exhausted
-    }
-    return *created > 0 ? 0 : (last_error ? last_error : 1);
-}
-
-// Makes sure both pools can serve about half of `num_pages` each.  New pages land on
-// either side at random, hence the over-allocation (sideaware.cu:1064-1080) and several
-// rounds before the caller falls back to cross-side mapping.
-int SaAllocator::top_up(size_t num_pages, bool compressed, void* stream, const SaAllocConfig& cfg) {
-    int rc = 0;
-    for (int round = 0; round < 4; ++round) {
-        // a block alternates sides page by page; the side it starts on takes the odd page
-        size_t need = (num_pages + 1) / 2 + (size_t)std::max(0, cfg.extra_required) / 2;
-        size_t have0 = pool_[compressed][0].size(), have1 = pool_[compressed][1].size();
-        size_t short0 = need > have0 ? need - have0 : 0, short1 = need > have1 ? need - have1 : 0;
-        size_t worst = std::max(short0, short1);
-        if (worst == 0) return 0;
-        // how often has a new page landed on the side we are short of? (1/2 on a balanced device)
-        int short_side = short1 > short0 ? 1 : 0;
-        double frac = (double)(seen_side_[short_side] + 1) / (double)(seen_side_[0] + seen_side_[1] + 2);
-        frac = std::min(0.5, std::max(0.05, frac));
-        size_t want = (size_t)((double)worst / frac * (round == 0 ? 1.0 : 1.15)) + (round == 0 ? (size_t)std::max(0, cfg.extra_alloc) : 2);
-        int created = 0;
-        rc = create_pages((int)std::min<size_t>(want, 1u << 30), compressed, stream, cfg, &created);
-        if (rc) return rc;
-    }
-    return 0;
-}
-
 void SaAllocator::release_pools() {
     for (int c = 0; c < 2; ++c)
         for (int s = 0; s < 2; ++s) {
@@ -190,13 +115,20 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
 // growing and shrinking the mapped set
 // ---------------------------------------------------------------------------
 
-// Maps a new segment of exactly `pages` pages whose first page is on side `phase`
-// and hands all of it out as one block.
+// Maps a new segment of exactly `pages` pages whose first page is on side `phase` and hands all
+// of it out as one block.
+//
+// Pages come from the per-side pools where they can.  The rest is created fresh and mapped
+// STRAIGHT INTO PLACE: only then can a page's side be measured, and about half of the fresh pages
+// turn out to sit in a slot of the right side already.  Misplaced ones are exchanged pairwise (a
+// side-1 page in a side-0 slot with a side-0 page in a side-1 slot); what cannot be paired goes
+// to the pool of its true side and its slot is filled in the next round.  The reference probes
+// every new page through a temporary mapping first (sideaware.cu:947-1019), which on B200 costs
+// one more cuMemSetAccess (~170 us) and cuMemUnmap (~90 us) per page than this does for the half
+// that lands well.
 uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg) {
-    top_up(pages, compressed, stream, cfg); // failure is handled below: we may still have enough pages
+    (void)cfg;
     auto& pools = pool_[compressed];
-    if (pools[0].size() + pools[1].size() < pages) return 0;
-
     std::unique_ptr<Segment> seg(new Segment());
     seg->compressed = compressed;
     seg->num_pages = pages;
@@ -205,36 +137,120 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
     seg->base = seg->reserved;
     if (side_bit(seg->base) != phase) seg->base += kSaPageBytes;
+    seg->pages.assign(pages, Page{0, 0});
+    auto slot_va = [&](size_t i) { return seg->base + i * kSaPageBytes; };
 
-    seg->pages.reserve(pages);
     bool ok = true;
+    std::vector<size_t> missing; // slots without a page yet
+    // 1) pooled pages of the matching side
     for (size_t i = 0; i < pages && ok; ++i) {
-        uint64_t va = seg->base + i * kSaPageBytes;
-        int want = side_bit(va);
-        int from = want;
-        if (pools[from].empty()) {
-            from ^= 1;
-            if (pools[from].empty()) { ok = false; break; }
-            if (!warned_cross_) {
-                std::fprintf(stderr, "sideaware: no free page on side %d, mapping a page of the other side (slower, still correct)\n", want);
-                warned_cross_ = true;
-            }
-            st_.cross_side_pages++;
-        }
-        Page pg = pools[from].back();
-        pools[from].pop_back();
-        if (be_->map_page(va, pg.handle)) {
+        const int want = side_bit(slot_va(i));
+        if (pools[want].empty()) { missing.push_back(i); continue; }
+        Page pg = pools[want].back();
+        pools[want].pop_back();
+        if (be_->map_page(slot_va(i), pg.handle)) {
             pools[pg.side].push_back(pg);
             ok = false;
             break;
         }
-        seg->pages.push_back(pg);
+        seg->pages[i] = pg;
     }
-    if (ok && be_->set_access(seg->base, pages * kSaPageBytes)) ok = false;
+    // access for what is mapped so far, in contiguous pieces (a range with holes cannot be opened at once)
+    auto open_ranges = [&](const std::vector<size_t>& slots) -> bool { // slots ascending
+        size_t k = 0;
+        while (k < slots.size()) {
+            size_t e = k;
+            while (e + 1 < slots.size() && slots[e + 1] == slots[e] + 1) ++e;
+            if (be_->set_access(slot_va(slots[k]), (e - k + 1) * kSaPageBytes)) return false;
+            k = e + 1;
+        }
+        return true;
+    };
+    if (ok) {
+        std::vector<size_t> pooled;
+        for (size_t i = 0; i < pages; ++i)
+            if (seg->pages[i].handle) pooled.push_back(i);
+        ok = open_ranges(pooled);
+    }
+    // 2) fresh pages, probed where they are
+    std::vector<uint64_t> vas;
+    std::vector<uint8_t> sides;
+    for (int round = 0; ok && !missing.empty() && round < 48; ++round) { // leftovers halve every round
+        std::vector<size_t> fresh;
+        for (size_t i : missing) {
+            uint64_t h = 0;
+            if (be_->create_page(&h, compressed)) break; // device memory exhausted: step 3 decides
+            if (be_->map_page(slot_va(i), h)) { be_->release_page(h); ok = false; break; }
+            seg->pages[i] = Page{h, 2}; // side unknown
+            fresh.push_back(i);
+            st_.pages_created++;
+        }
+        if (!ok || fresh.empty()) break;
+        if (!open_ranges(fresh)) { ok = false; break; }
+        vas.clear();
+        for (size_t i : fresh) vas.push_back(slot_va(i));
+        sides.assign(fresh.size(), 0);
+        if (be_->probe_pages(vas.data(), (int)fresh.size(), sides.data(), stream)) { ok = false; break; }
+        std::vector<size_t> wrong[2]; // wrong[w]: slots that want side w and hold a page of side 1 - w
+        for (size_t k = 0; k < fresh.size(); ++k) {
+            const size_t i = fresh[k];
+            seg->pages[i].side = sides[k] & 1;
+            const int want = side_bit(slot_va(i));
+            if ((int)seg->pages[i].side != want) wrong[want].push_back(i);
+        }
+        // exchange misplaced pages pairwise
+        while (ok && !wrong[0].empty() && !wrong[1].empty()) {
+            const size_t i = wrong[0].back(), j = wrong[1].back();
+            wrong[0].pop_back();
+            wrong[1].pop_back();
+            be_->unmap_page(slot_va(i));
+            be_->unmap_page(slot_va(j));
+            std::swap(seg->pages[i], seg->pages[j]);
+            if (be_->map_page(slot_va(i), seg->pages[i].handle)) { pools[seg->pages[i].side].push_back(seg->pages[i]); seg->pages[i] = Page{0, 0}; ok = false; }
+            if (be_->map_page(slot_va(j), seg->pages[j].handle)) { pools[seg->pages[j].side].push_back(seg->pages[j]); seg->pages[j] = Page{0, 0}; ok = false; }
+            if (ok && (be_->set_access(slot_va(i), kSaPageBytes) || be_->set_access(slot_va(j), kSaPageBytes))) ok = false;
+        }
+        // what is left over is all of one kind: those pages wait in the pool of their true side
+        std::vector<size_t> still;
+        for (int w = 0; w < 2; ++w)
+            for (size_t i : wrong[w]) {
+                be_->unmap_page(slot_va(i));
+                pools[seg->pages[i].side].push_back(seg->pages[i]);
+                seg->pages[i] = Page{0, 0};
+                still.push_back(i);
+            }
+        // slots for which no page could be created stay missing too
+        for (size_t i : missing)
+            if (!seg->pages[i].handle && std::find(still.begin(), still.end(), i) == still.end()) still.push_back(i);
+        std::sort(still.begin(), still.end());
+        missing.swap(still);
+    }
+    // 3) no page of the right side to be had: one of the other side still works, only slower
+    if (ok && !missing.empty()) {
+        std::vector<size_t> crossed;
+        for (size_t i : missing) {
+            const int other = side_bit(slot_va(i)) ^ 1;
+            if (pools[other].empty()) { ok = false; break; }
+            if (!warned_cross_) {
+                std::fprintf(stderr, "sideaware: no free page on side %d, mapping a page of the other side (slower, still correct)\n", other ^ 1);
+                warned_cross_ = true;
+            }
+            Page pg = pools[other].back();
+            pools[other].pop_back();
+            if (be_->map_page(slot_va(i), pg.handle)) { pools[pg.side].push_back(pg); ok = false; break; }
+            seg->pages[i] = pg;
+            st_.cross_side_pages++;
+            crossed.push_back(i);
+        }
+        if (ok) ok = open_ranges(crossed);
+    }
     if (!ok) {
-        for (size_t i = 0; i < seg->pages.size(); ++i) {
-            be_->unmap_page(seg->base + i * kSaPageBytes);
-            pools[seg->pages[i].side].push_back(seg->pages[i]);
+        for (size_t i = 0; i < pages; ++i) {
+            Page& pg = seg->pages[i];
+            if (!pg.handle) continue;
+            be_->unmap_page(slot_va(i));
+            if (pg.side <= 1) pools[pg.side].push_back(pg);
+            else be_->release_page(pg.handle); // never measured: give it back
         }
         be_->free_va(seg->reserved, seg->reserved_bytes);
         return 0;

@@ -50,8 +50,8 @@ struct SaBackend {
     virtual int map_page(uint64_t va, uint64_t handle) = 0;
     virtual void unmap_page(uint64_t va) = 0;
     virtual int set_access(uint64_t va, size_t bytes) = 0;
-    // side (0/1) of byte 0 of `n` consecutive mapped pages starting at `va`
-    virtual int probe_pages(uint64_t va, int n, uint8_t* sides, void* stream) = 0;
+    // side (0/1) of byte 0 of each of the `n` mapped, accessible pages at the addresses `vas`
+    virtual int probe_pages(const uint64_t* vas, int n, uint8_t* sides, void* stream) = 0;
     virtual void device_sync() = 0;
     virtual void stream_sync(void* stream) = 0;
 };
@@ -59,10 +59,9 @@ struct SaBackend {
 struct SaAllocConfig {
     size_t trim_start = 16ull << 30; // when the mapped set must grow and more than this is free-but-mapped, unmap
     size_t trim_end = 2ull << 30;    // ... least recently freed runs down to this
-    int extra_required = 1;
-    int extra_alloc = 10;
+    int extra_required = 1;          // accepted for compatibility with the reference's setter; pages are
+    int extra_alloc = 10;            // created on demand, straight into the segment that needs them
     bool compression = false;
-    int max_probe_batch = 1024;      // pages probed per temporary mapping
 };
 
 struct SaAllocStats {
@@ -113,8 +112,6 @@ private:
         void* stream = nullptr;
     };
 
-    int top_up(size_t num_pages, bool compressed, void* stream, const SaAllocConfig& cfg);
-    int create_pages(int count, bool compressed, void* stream, const SaAllocConfig& cfg, int* created);
     uint64_t take_from_free(size_t pages, int phase, bool compressed, void* stream);
     uint64_t grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg);
     void insert_free(uint64_t va, Run run);
@@ -136,7 +133,6 @@ private:
     std::unordered_map<size_t, int> phase_;
     size_t cached_bytes_ = 0, live_bytes_ = 0;
     uint64_t seq_ = 0;
-    uint64_t seen_side_[2] = {0, 0}; // sides of all pages ever created
     bool warned_cross_ = false;
     SaAllocStats st_;
 };

@@ -117,14 +117,12 @@ public:
         acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
         return (int)d_->MemSetAccess((CUdeviceptr)va, bytes, &acc, 1);
     }
-    int probe_pages(uint64_t va, int n, uint8_t* sides, void* /*stream*/) override {
+    int probe_pages(const uint64_t* vas, int n, uint8_t* sides, void* /*stream*/) override {
         ScopedTime st(T_PROBE);
         // fresh pages have no pending work: probe on the library's own stream so the
         // caller's stream is not drained
-        std::vector<uint64_t> addrs(n);
-        for (int i = 0; i < n; ++i) addrs[i] = va + (uint64_t)i * kSaPageBytes;
         int ambiguous = 0;
-        cudaError_t e = sa_probe_sides(dev_->probe, dev_->topo, addrs.data(), n, sides, dev_->probe_stream, &ambiguous);
+        cudaError_t e = sa_probe_sides(dev_->probe, dev_->topo, vas, n, sides, dev_->probe_stream, &ambiguous);
         return e == cudaSuccess ? 0 : 1000 + (int)e;
     }
     void device_sync() override {

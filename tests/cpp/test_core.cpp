@@ -201,12 +201,11 @@ struct FakeDriver : SaBackend {
         }
         return 0;
     }
-    int probe_pages(uint64_t va, int n, uint8_t* sides, void*) override {
+    int probe_pages(const uint64_t* vas, int n, uint8_t* sides, void*) override {
         if (tick(fail_probe_after)) return 1;
         for (int i = 0; i < n; ++i) {
-            uint64_t a = va + (uint64_t)i * kSaPageBytes;
-            CHECK(accessible.count(a) == 1);
-            sides[i] = (uint8_t)page_side[mappings[a]];
+            CHECK(accessible.count(vas[i]) == 1);
+            sides[i] = (uint8_t)page_side[mappings[vas[i]]];
         }
         return 0;
     }
