@@ -148,3 +148,32 @@ def test_concurrent_malloc_free(sa):
         t.join()
     assert not errors, errors
     assert sa.stats()["bytes_mapped_live"] == 0
+
+
+def test_compressible_memory_option(sa):
+    """sideaware_compression(true): pages are created compressible where the device supports it
+    (sideaware.cu:817-834, :940); kept apart from plain pages; data round-trips unchanged."""
+    n = 24 * MiB
+    data = np.random.default_rng(3).integers(0, 256, size=n, dtype=np.uint8)
+    data[: n // 2] = 0  # compressible half
+    plain = sa.malloc(n)
+    sa.lib.sideaware_compression(True)
+    try:
+        a = sa.malloc(n)
+        b = sa.malloc(n)
+        assert a % (2 * MiB) == 0 and a != plain
+        ch.h2d(a, data)
+        sa.memcpy_ptr(b, a, n)
+        ch.sync()
+        assert np.array_equal(ch.d2h(b, n), data)
+        sa.free(a)
+        sa.free(b)
+    finally:
+        sa.lib.sideaware_compression(False)
+    c = sa.malloc(n)  # plain again
+    ch.h2d(c, data)
+    ch.sync()
+    assert np.array_equal(ch.d2h(c, n), data)
+    sa.free(c)
+    sa.free(plain)
+    assert sa.error_count() == 0, sa.last_error()
