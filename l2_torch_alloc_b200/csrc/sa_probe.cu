@@ -174,28 +174,31 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
     int smem = (int)std::min<size_t>(prop.sharedMemPerBlockOptin, 120 * 1024);
     if (smem > 48 * 1024) cudaFuncSetAttribute(sa_discover_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
 
+    // Latencies are kept as minima over all passes (noise - another process on the GPU, a clock ramp -
+    // only ever adds latency), so a pass that leaves doubts is simply followed by another one.
     std::vector<uint32_t> h_lat((size_t)SA_MAX_SM * kNumAddr), h_seen(SA_MAX_SM);
-    for (int attempt = 0; attempt < 4; ++attempt) {
+    for (int pass = 0; pass < 4; ++pass) {
         sa_discover_kernel<<<2 * topo->num_sms, 32, smem>>>(p->page, p->offsets, kNumAddr, p->lat, p->seen, 0u, kDiscoverReps, kChain);
         if ((e = cudaGetLastError()) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "launch sa_discover_kernel"); }
         if ((e = cudaDeviceSynchronize()) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "sa_discover_kernel"); }
-        cudaMemcpy(h_seen.data(), p->seen, sz_seen, cudaMemcpyDeviceToHost);
-        int seen = 0;
-        for (int i = 0; i < SA_MAX_SM; ++i) seen += h_seen[i] != 0;
-        if (seen >= topo->num_sms) break;
+        if ((e = cudaMemcpy(h_seen.data(), p->seen, sz_seen, cudaMemcpyDeviceToHost)) != cudaSuccess ||
+            (e = cudaMemcpy(h_lat.data(), p->lat, sz_lat, cudaMemcpyDeviceToHost)) != cudaSuccess) {
+            sa_probe_destroy(p);
+            return fail(e, "download latencies");
+        }
+        std::vector<uint32_t> rows;
+        std::vector<int> row_smid;
+        topo->max_smid = -1;
+        for (int sm = 0; sm < SA_MAX_SM; ++sm) {
+            if (!h_seen[sm]) continue;
+            topo->max_smid = sm;
+            row_smid.push_back(sm);
+            rows.insert(rows.end(), h_lat.begin() + (size_t)sm * kNumAddr, h_lat.begin() + (size_t)(sm + 1) * kNumAddr);
+        }
+        sa_analyse_latency_matrix(rows, (int)row_smid.size(), row_smid, offsets, topo);
+        topo->discovery_passes = pass + 1;
+        if ((int)row_smid.size() >= topo->num_sms && topo->hash_usable && topo->confidence >= 0.95) break;
     }
-    if ((e = cudaMemcpy(h_lat.data(), p->lat, sz_lat, cudaMemcpyDeviceToHost)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "download latencies"); }
-
-    std::vector<uint32_t> rows;
-    std::vector<int> row_smid;
-    topo->max_smid = -1;
-    for (int sm = 0; sm < SA_MAX_SM; ++sm) {
-        if (!h_seen[sm]) continue;
-        topo->max_smid = sm;
-        row_smid.push_back(sm);
-        rows.insert(rows.end(), h_lat.begin() + (size_t)sm * kNumAddr, h_lat.begin() + (size_t)(sm + 1) * kNumAddr);
-    }
-    sa_analyse_latency_matrix(rows, (int)row_smid.size(), row_smid, offsets, topo);
     if ((e = cudaMemcpy(p->gpu_side_index, topo->side_index, SA_MAX_SM, cudaMemcpyHostToDevice)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "upload side index"); }
     *out = p;
     return cudaSuccess;

@@ -14,6 +14,7 @@ struct SaTopology {
     int device = -1;
     int num_sms = 0;
     int sms_seen = 0;
+    int discovery_passes = 0;     // probe kernel launches it took (more than 1 = the first pass left doubts)
     int max_smid = -1;
     uint8_t side_index[SA_MAX_SM] = {0}; // byte = side | ordinal << 1 (the reference's format, sideaware.cu:669-675)
     int count[2] = {0, 0};
