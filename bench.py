@@ -442,9 +442,13 @@ def run_ours(args, ranks):
         lib.sideaware_memcpy(dst, src, MEMCPY_BYTES, dev, sp)
 
     sa.set_placement("aware")
+    # the timed region: K launches back to back, one event before and one after (an event between two
+    # launches would keep consecutive kernels from overlapping launch and tail)
     with ClockSampler(dev) as clocks:
-        total_ms, each = time_launches(torch, step, args.steps, args.warmup, ranks, per_launch=True)
-    launches = sa.stats()["kernel_launches"] - launches_before - args.warmup
+        total_ms, _ = time_launches(torch, step, args.steps, args.warmup, ranks, per_launch=False)
+    launches = sa.stats()["kernel_launches"] - launches_before - args.warmup  # counted by the library itself
+    # a second, untimed-for-the-metric pass with an event after every launch, for best / median launch times
+    _, each = time_launches(torch, step, min(args.steps, 50), 3, None, per_launch=True)
     worst_ms = ranks.max(total_ms)
     value = ranks.world * args.steps * 2 * MEMCPY_BYTES / (worst_ms * 1e-3) / 1e9
     # parity spot check of what was just timed
@@ -456,7 +460,7 @@ def run_ours(args, ranks):
     del back
 
     peak, peak_kind = measured_peak()
-    avg_launch_ms = statistics.mean(each)
+    avg_launch_ms = total_ms / args.steps  # average launch duration over the timed region of this rank
     achieved = gbs(2 * MEMCPY_BYTES, avg_launch_ms)
     engine = lib.sideaware_get_memcpy_engine()
     roofline = {"bound": "hbm", "kernel": "sa_memcpy_bulk_kernel" if engine == 1 else "sa_memcpy_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",

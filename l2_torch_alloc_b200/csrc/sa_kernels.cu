@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "sa_kernels.hpp"
@@ -241,9 +243,25 @@ sa_silu_mul_kernel(const __grid_constant__ SaSched s, const __grid_constant__ Sa
 
 } // namespace
 
+SaLaunch::SaLaunch(int grid, int threads, size_t smem, cudaStream_t stream) {
+    static const bool pdl = [] { // on unless SIDEAWARE_PDL=0
+        const char* e = std::getenv("SIDEAWARE_PDL");
+        return !(e && std::atoi(e) == 0);
+    }();
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+}
+
 cudaError_t sa_launch_memcpy(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* dst, const void* src, cudaStream_t stream) {
-    sa_memcpy_kernel<<<grid, threads, 0, stream>>>(s, sides, (uint4*)dst, (const uint4*)src);
-    return cudaGetLastError();
+    SaLaunch l(grid, threads, 0, stream);
+    return cudaLaunchKernelEx(&l.cfg, sa_memcpy_kernel, s, sides, (uint4*)dst, (const uint4*)src);
 }
 
 cudaError_t sa_launch_rope(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* x, const float* table,
@@ -252,15 +270,15 @@ cudaError_t sa_launch_rope(const SaSched& s, const SaSideTable& sides, int grid,
     // ~72; a 1024-thread block would cap it at 64 and spill), and 24 warps x 4 KiB still keep
     // 96 KiB in flight per SM
     if (threads > 768) return cudaErrorInvalidConfiguration;
-    if (bf16) sa_rope_kernel<true, 768><<<grid, threads, 0, stream>>>(s, sides, (uint4*)x, (const float4*)table, sh);
-    else sa_rope_kernel<false, 768><<<grid, threads, 0, stream>>>(s, sides, (uint4*)x, (const float4*)table, sh);
-    return cudaGetLastError();
+    SaLaunch l(grid, threads, 0, stream);
+    if (bf16) return cudaLaunchKernelEx(&l.cfg, sa_rope_kernel<true, 768>, s, sides, (uint4*)x, (const float4*)table, sh);
+    return cudaLaunchKernelEx(&l.cfg, sa_rope_kernel<false, 768>, s, sides, (uint4*)x, (const float4*)table, sh);
 }
 
 cudaError_t sa_launch_silu_mul(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream) {
-    sa_silu_mul_kernel<<<grid, threads, 0, stream>>>(s, sides, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
-    return cudaGetLastError();
+    SaLaunch l(grid, threads, 0, stream);
+    return cudaLaunchKernelEx(&l.cfg, sa_silu_mul_kernel, s, sides, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
 }
 
 // ---------------------------------------------------------------------------

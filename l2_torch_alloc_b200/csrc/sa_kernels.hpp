@@ -30,3 +30,13 @@ cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int de
 cudaError_t sa_launch_memcpy_bulk(const SaSched& s, const SaSideTable& sides, int grid, void* dst, const void* src,
                                   cudaStream_t stream);
 int sa_memcpy_bulk_warps();
+
+// Launch configuration shared by the ahead-of-time kernels.  Unless SIDEAWARE_PDL=0 the launch carries the
+// programmatic-stream-serialization attribute: when two of this library's kernels follow each other on a
+// stream, the second one's launch and prologue overlap the first one's tail; it touches data only after the
+// first has completed (griddepcontrol.wait in sa_for_each_chunk).  Measured: +3 % at 256 MiB, +1 % at 1 GiB.
+struct SaLaunch {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    SaLaunch(int grid, int threads, size_t smem, cudaStream_t stream);
+};

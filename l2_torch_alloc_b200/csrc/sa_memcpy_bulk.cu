@@ -161,8 +161,8 @@ cudaError_t launch_cfg(const SaSched& s, const SaSideTable& sides, int grid, voi
         const char* e = std::getenv("SIDEAWARE_BULK_HINTS");
         return e ? std::atoi(e) & 3 : 0;
     }();
-    sa_memcpy_bulk_kernel<WARPS, S><<<grid, WARPS * 32, smem, stream>>>(s, sides, (uint4*)dst, (const uint4*)src, hints);
-    return cudaGetLastError();
+    SaLaunch l(grid, WARPS * 32, smem, stream);
+    return cudaLaunchKernelEx(&l.cfg, sa_memcpy_bulk_kernel<WARPS, S>, s, sides, (uint4*)dst, (const uint4*)src, hints);
 }
 
 // default shape; SIDEAWARE_BULK_CFG=<n> picks another one for tuning

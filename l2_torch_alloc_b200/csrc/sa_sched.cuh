@@ -196,10 +196,16 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
         return r;
     };
 
+    // Programmatic dependent launch: let the next kernel of the stream start its own prologue as
+    // soon as this grid's blocks have all come this far, and do not touch data before the previous
+    // kernel has completed and flushed.  Both are no-ops for launches without that attribute.  The
+    // opening claim only touches this launch's own ticket slot, so it may precede the wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         sa_drained = 0u;
         sa_batch = atomicAdd(own, s.active_warps * s.share);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
     const sa_u32 base = sa_batch;
     // One loop with a single place where tickets are worked on (the body is inlined once):
