@@ -561,7 +561,14 @@ def run_ours(args, ranks):
             f = lambda: lib.sideaware_memcpy(b, a, n, dev, sp)  # noqa: E731
             reps = 40 if n <= (256 << 20) else 10
             ms, ea = time_launches(torch, f, reps, 3, None, per_launch=True)
-            sweep[str(n)] = {"gbs": gbs(2 * n, statistics.median(ea)), "us": statistics.median(ea) * 1e3}
+            # back to back (no event between launches; events cost ~2 us each and are only 2 us fine)
+            tot, _ = time_launches(torch, f, reps, 3, None, per_launch=False)
+            g = lambda: rt.cudaMemcpyAsync(b, a, n, 3, sp)  # noqa: E731
+            tot_rt, _ = time_launches(torch, g, reps, 3, None, per_launch=False)
+            sweep[str(n)] = {"gbs": gbs(2 * n, statistics.median(ea)), "us": statistics.median(ea) * 1e3,
+                             "back_to_back_us": tot / reps * 1e3, "back_to_back_gbs": gbs(2 * n, tot / reps),
+                             "cudaMemcpyAsync_back_to_back_us": tot_rt / reps * 1e3,
+                             "cudaMemcpyAsync_back_to_back_gbs": gbs(2 * n, tot_rt / reps)}
             lib.sideaware_free_auto(a, n, dev, sp)
             lib.sideaware_free_auto(b, n, dev, sp)
         lib.sideaware_alloc_threshold(8 << 20)

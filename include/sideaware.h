@@ -119,6 +119,16 @@ sideaware_status_t sideaware_rope_backward(void* dqkv, const float* freqs_cis,
                                            int B, int T, int Nq, int Nkv, int HS, int dtype,
                                            int device, sideaware_stream_t stream);
 
+/* Fills the cos/sin table the two calls above read, freqs_cis[end][dim/2][2] fp32, in
+ * device memory.  Takes the place of the host function precompute_freqs_cis
+ * (example_llmc_rope.cu:19-52): the dim/2 frequencies (with the llama-3 wavelength
+ * rescale when use_scaled != 0) are computed on the host with the reference's fp32
+ * expression, the end * dim/2 angles t * freq in fp32 on the GPU, their cosine and sine
+ * in fp64 rounded once to fp32 (within 1 fp32 ulp of the reference's cosf/sinf, equal
+ * in nearly every entry).  dim even, 2 <= dim <= 1024. */
+sideaware_status_t sideaware_rope_precompute_freqs(float* freqs_cis, int dim, int end, float theta,
+                                                   int use_scaled, int device, sideaware_stream_t stream);
+
 /* out = bf16(a * sigmoid(a) * b * scale), n elements (multiple of 8), the
  * ahead-of-time build of the benchmark's example functor. */
 sideaware_status_t sideaware_silu_mul_bf16(void* out, const void* a, const void* b, float scale,

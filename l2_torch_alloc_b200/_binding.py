@@ -60,6 +60,7 @@ SIGNATURES = {
     "sideaware_error_count": (c.c_ulonglong, []),
     "sideaware_rope_forward": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sideaware_rope_backward": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "sideaware_rope_precompute_freqs": (_i, [_vp, _i, _i, c.c_float, _i, _i, _vp]),
     "sideaware_silu_mul_bf16": (_i, [_vp, _vp, _vp, c.c_float, _sz, _i, _vp]),
     "sideaware_compile_check": (_i, [c.c_char_p, _i, c.c_char_p, _sz]),
     "sideaware_set_placement": (None, [_i]),

@@ -106,6 +106,12 @@ class SideAware:
         if rc != 0:
             raise RuntimeError(f"sideaware_rope_forward failed with CUDA error {rc}: {self.last_error()}")
 
+    def rope_precompute_freqs_ptr(self, table: int, dim: int, end: int, theta: float, use_scaled: bool,
+                                  device: int = 0, stream=None) -> None:
+        rc = self.lib.sideaware_rope_precompute_freqs(table, dim, end, theta, 1 if use_scaled else 0, device, _stream_ptr(stream))
+        if rc != 0:
+            raise RuntimeError(f"sideaware_rope_precompute_freqs failed with CUDA error {rc}: {self.last_error()}")
+
     def silu_mul_ptr(self, out: int, a: int, b: int, scale: float, n: int, device: int = 0, stream=None) -> None:
         rc = self.lib.sideaware_silu_mul_bf16(out, a, b, scale, n, device, _stream_ptr(stream))
         if rc != 0:
@@ -204,6 +210,15 @@ class SideAware:
         assert H == n_q_heads + 2 * n_kv_heads and tuple(freqs_cis.shape) == (T, HS // 2, 2)
         self.rope_backward_ptr(dqkv.data_ptr(), freqs_cis.data_ptr(), B, T, n_q_heads, n_kv_heads, HS,
                                dqkv.dtype == torch.bfloat16, dqkv.device.index, torch.cuda.current_stream(dqkv.device))
+
+    def rope_precompute_freqs(self, dim: int, end: int, theta: float = 10000.0, use_scaled: bool = False, device=None):
+        """The fp32 table [end, dim/2, 2] of (cos, sin) that rope_forward / rope_backward read, made on the GPU."""
+        import torch
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        table = torch.empty((end, dim // 2, 2), dtype=torch.float32, device=device)
+        self.rope_precompute_freqs_ptr(table.data_ptr(), dim, end, float(theta), use_scaled, device.index,
+                                       torch.cuda.current_stream(device))
+        return table
 
     def silu_mul(self, out, a, b, scale: float) -> None:
         import torch

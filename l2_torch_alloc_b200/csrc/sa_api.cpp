@@ -1,6 +1,7 @@
 // extern "C" surface of sideaware.so (declarations and reference citations: include/sideaware.h).
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstring>
 #include <random>
 
@@ -175,12 +176,12 @@ SA_API void sideaware_elementwise(int kernel_id, size_t num_bytes,
             return;
         }
         if (sa_config().memcpy_engine.load() == 1) {
-            sa_prepare_launch(dev, (uint64_t)in0, num_vecs, 0, forced_per_side, false, &s, &grid, &threads, sa_memcpy_bulk_warps());
+            if (!sa_prepare_launch(dev, stream, (uint64_t)in0, num_vecs, 0, forced_per_side, false, &s, &grid, &threads, sa_memcpy_bulk_warps())) return;
             e = sa_launch_memcpy_bulk(s, dev->side_table, grid, out0, in0, (cudaStream_t)stream);
             if (e != cudaSuccess) sa_set_error("sideaware_memcpy (bulk engine) launch: %s", cudaGetErrorString(e));
             return;
         }
-        sa_prepare_launch(dev, (uint64_t)in0, num_vecs, parallel_groups, forced_per_side, false, &s, &grid, &threads);
+        if (!sa_prepare_launch(dev, stream, (uint64_t)in0, num_vecs, parallel_groups, forced_per_side, false, &s, &grid, &threads)) return;
         e = sa_launch_memcpy(s, dev->side_table, grid, threads, out0, in0, (cudaStream_t)stream);
         if (e != cudaSuccess) sa_set_error("sideaware_memcpy launch: %s", cudaGetErrorString(e));
         return;
@@ -189,7 +190,7 @@ SA_API void sideaware_elementwise(int kernel_id, size_t num_bytes,
     // geometry is redone inside the kernel for whichever array it moves as 16-byte vectors;
     // the host only needs the size to pick grid and ticket length
     const void* track = in0 ? in0 : out0;
-    sa_prepare_launch(dev, (uint64_t)track, num_vecs, groups, forced_per_side, false, &s, &grid, &threads);
+    if (!sa_prepare_launch(dev, stream, (uint64_t)track, num_vecs, groups, forced_per_side, false, &s, &grid, &threads)) return;
     bool misaligned = ((uintptr_t)in0 % kSaPageBytes) || ((uintptr_t)out0 % kSaPageBytes);
     bool wide = misaligned || num_bytes >= (2ull << 30); // same rule as sideaware.cu:1386-1388
     void* outs[4] = {out0, out1, out2, out3};
@@ -255,9 +256,43 @@ static sideaware_status_t rope_launch(void* qkv, const float* freqs_cis, int B, 
     SaSched s;
     int grid = 0, threads = 0;
     // 768 threads per block: the rotation needs ~70 registers, measured faster than 1024 threads with spills
-    sa_prepare_launch(dev, (uint64_t)qkv, num_vecs, 3, 0, false, &s, &grid, &threads);
+    if (!sa_prepare_launch(dev, stream, (uint64_t)qkv, num_vecs, 3, 0, false, &s, &grid, &threads)) return cudaErrorMemoryAllocation;
     cudaError_t e = sa_launch_rope(s, dev->side_table, grid, threads, qkv, freqs_cis, sh, dtype == 1, (cudaStream_t)stream);
     if (e != cudaSuccess) sa_set_error("sideaware_rope_forward launch: %s", cudaGetErrorString(e));
+    return e;
+}
+
+// Frequency of pair i: theta^(-2i/dim) in fp32, then the llama-3 context-extension rule
+// (wavelengths above the original 8192-token context slowed 8x, those below a quarter of it
+// kept, a linear blend in between).  Same fp32/fp64 mix, operation by operation, as
+// precompute_freqs_cis (example_llmc_rope.cu:24-43), so the values are the reference's bit for bit.
+static float rope_pair_frequency(int i, int dim, float theta, bool use_scaled) {
+    float freq = 1.0f / powf(theta, (float)(2 * i) / dim);
+    if (!use_scaled) return freq;
+    const float slow_down = 8.0f, long_wave = 8192.0f, short_wave = 8192.0f / 4.0f;
+    const float wavelen = (float)((double)2.0f * 3.14159265358979323846 / (double)freq);
+    if (wavelen < short_wave) return freq;
+    if (wavelen > long_wave) return freq / slow_down;
+    const float blend = (8192.0f / wavelen - 1.0f) / 3.0f;
+    const float kept = blend * freq;
+    return (1.0f - blend) * freq / slow_down + kept;
+}
+
+SA_API sideaware_status_t sideaware_rope_precompute_freqs(float* freqs_cis, int dim, int end, float theta,
+                                                          int use_scaled, int device, sideaware_stream_t stream) {
+    if (!freqs_cis || dim < 2 || dim > 1024 || (dim & 1) || end <= 0 || !(theta > 0.0f)) {
+        sa_set_error("sideaware_rope_precompute_freqs: invalid argument (dim %d, end %d, theta %g)", dim, end, (double)theta);
+        return cudaErrorInvalidValue;
+    }
+    const void* ptrs[1] = {freqs_cis};
+    if (!check_launch_args("sideaware_rope_precompute_freqs", 16, ptrs, 1)) return cudaErrorInvalidValue;
+    SaDevice* dev = sa_device(device);
+    if (!dev) return cudaErrorInitializationError;
+    SaScopedDevice guard(dev->id);
+    float freqs[512];
+    for (int i = 0; i < dim / 2; ++i) freqs[i] = rope_pair_frequency(i, dim, theta, use_scaled != 0);
+    cudaError_t e = sa_launch_rope_table(freqs_cis, freqs, dim / 2, end, (cudaStream_t)stream);
+    if (e != cudaSuccess) sa_set_error("sideaware_rope_precompute_freqs launch: %s", cudaGetErrorString(e));
     return e;
 }
 
@@ -275,7 +310,7 @@ SA_API sideaware_status_t sideaware_silu_mul_bf16(void* out, const void* a, cons
     SaScopedDevice guard(dev->id);
     SaSched s;
     int grid = 0, threads = 0;
-    sa_prepare_launch(dev, (uint64_t)a, n / 8, 0, 0, false, &s, &grid, &threads);
+    if (!sa_prepare_launch(dev, stream, (uint64_t)a, n / 8, 0, 0, false, &s, &grid, &threads)) return cudaErrorMemoryAllocation;
     cudaError_t e = sa_launch_silu_mul(s, dev->side_table, grid, threads, out, a, b, scale, (cudaStream_t)stream);
     if (e != cudaSuccess) sa_set_error("sideaware_silu_mul_bf16 launch: %s", cudaGetErrorString(e));
     return e;

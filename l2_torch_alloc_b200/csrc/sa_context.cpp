@@ -282,7 +282,7 @@ std::vector<SaDevice*> sa_initialised_devices() {
     return out;
 }
 
-void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
+bool sa_prepare_launch(SaDevice* dev, void* stream, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
                        int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads, int exact_warps) {
     std::memset(s, 0, sizeof(*s));
     int groups = parallel_groups > 0 ? parallel_groups : 4;
@@ -299,7 +299,13 @@ void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, in
     s->dc_per_ticket = 0;
     sa_sched_geometry(*s, track_addr, num_vecs, (uint32_t)(g * warps / 2));
     sa_sched_grid(*s, g, warps, &g);
-    s->tickets = sa_probe_ticket_slot(dev->probe);
+    bool overlap = false;
+    s->tickets = sa_probe_ticket_slot(dev->probe, stream, &overlap);
+    if (!s->tickets) {
+        sa_set_error("no ticket slot for stream %p on device %d (device memory exhausted, or a new stream first used while capturing)", stream, dev->id);
+        return false;
+    }
+    s->overlap = overlap ? 1u : 0u;
     s->hash = dev->full_hash;
     int placement = sa_config().placement.load();
     s->placement = dev->full_hash ? (uint32_t)placement : (uint32_t)SA_PLACE_UNAWARE;
@@ -307,6 +313,7 @@ void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, in
     *grid = g;
     *threads = warps * 32;
     dev->launches.fetch_add(1);
+    return true;
 }
 
 SaDevice* sa_device_if_ready(int device) {

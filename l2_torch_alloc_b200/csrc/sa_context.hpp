@@ -69,8 +69,9 @@ const char* sa_last_error_text();
 unsigned long long sa_error_total();
 
 // Fills the launch-constant scheduling state for an array of `num_vecs` 16-byte vectors
-// whose side-tracking array starts at `track_addr`, and picks grid and block size.
-void sa_prepare_launch(SaDevice* dev, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
+// whose side-tracking array starts at `track_addr`, and picks grid and block size.  The ticket
+// slot comes from the ring of `stream`.  False (error recorded) if no slot could be had.
+bool sa_prepare_launch(SaDevice* dev, void* stream, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
                        int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads,
                        int exact_warps = 0); // exact_warps > 0: that many warps per block, whatever the groups say
 

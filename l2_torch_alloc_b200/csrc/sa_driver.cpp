@@ -38,6 +38,7 @@ void load() {
     SA_SYM(ModuleUnload, "cuModuleUnload");
     SA_SYM(ModuleGetFunction, "cuModuleGetFunction");
     SA_SYM(LaunchKernel, "cuLaunchKernel");
+    SA_SYM(LaunchKernelEx, "cuLaunchKernelEx");
 #undef SA_SYM
     g_ok = ok;
 }

@@ -22,6 +22,7 @@ struct SaDriver {
     CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*);
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                              CUstream, void**, void**);
+    CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**);
 };
 
 // nullptr (and *why filled) when libcuda.so.1 or one of the symbols is missing.

@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "sa_context.hpp"
+#include "sa_kernels.hpp"
 
 #include "_gen/sa_embedded_sources.inc" // kSaSchedSource, kSaJitTemplateSource
 
@@ -276,9 +277,20 @@ cudaError_t sa_jit_launch(SaDevice* dev, int id, bool wide, const SaSched& sched
         an.val = val;
         params[2] = &an;
     }
-    CUresult r = dev->drv->LaunchKernel(fn, (unsigned)grid, 1, 1, (unsigned)threads, 1, 1, 0, (CUstream)stream, params, nullptr);
+    // same launch attribute as the ahead-of-time kernels (SaLaunch)
+    CUlaunchConfig cfg{};
+    cfg.gridDimX = (unsigned)grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = (unsigned)threads; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = 0;
+    cfg.hStream = (CUstream)stream;
+    CUlaunchAttribute attr[1];
+    attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr[0].value.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (sa_pdl_enabled() && s.overlap) ? 1 : 0;
+    CUresult r = dev->drv->LaunchKernelEx(&cfg, fn, params, nullptr);
     if (r != CUDA_SUCCESS) {
-        *why = "cuLaunchKernel: " + sa_cu_error(dev->drv, r);
+        *why = "cuLaunchKernelEx: " + sa_cu_error(dev->drv, r);
         return cudaErrorLaunchFailure;
     }
     return cudaSuccess;

@@ -243,11 +243,16 @@ sa_silu_mul_kernel(const __grid_constant__ SaSched s, const __grid_constant__ Sa
 
 } // namespace
 
-SaLaunch::SaLaunch(int grid, int threads, size_t smem, cudaStream_t stream) {
+bool sa_pdl_enabled() {
     static const bool pdl = [] { // on unless SIDEAWARE_PDL=0
         const char* e = std::getenv("SIDEAWARE_PDL");
         return !(e && std::atoi(e) == 0);
     }();
+    return pdl;
+}
+
+SaLaunch::SaLaunch(const SaSched& s, int grid, int threads, size_t smem, cudaStream_t stream) {
+    const bool pdl = sa_pdl_enabled();
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)threads);
@@ -256,11 +261,11 @@ SaLaunch::SaLaunch(int grid, int threads, size_t smem, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = (pdl && s.overlap) ? 1 : 0;
 }
 
 cudaError_t sa_launch_memcpy(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* dst, const void* src, cudaStream_t stream) {
-    SaLaunch l(grid, threads, 0, stream);
+    SaLaunch l(s, grid, threads, 0, stream);
     return cudaLaunchKernelEx(&l.cfg, sa_memcpy_kernel, s, sides, (uint4*)dst, (const uint4*)src);
 }
 
@@ -270,15 +275,49 @@ cudaError_t sa_launch_rope(const SaSched& s, const SaSideTable& sides, int grid,
     // ~72; a 1024-thread block would cap it at 64 and spill), and 24 warps x 4 KiB still keep
     // 96 KiB in flight per SM
     if (threads > 768) return cudaErrorInvalidConfiguration;
-    SaLaunch l(grid, threads, 0, stream);
+    SaLaunch l(s, grid, threads, 0, stream);
     if (bf16) return cudaLaunchKernelEx(&l.cfg, sa_rope_kernel<true, 768>, s, sides, (uint4*)x, (const float4*)table, sh);
     return cudaLaunchKernelEx(&l.cfg, sa_rope_kernel<false, 768>, s, sides, (uint4*)x, (const float4*)table, sh);
 }
 
 cudaError_t sa_launch_silu_mul(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream) {
-    SaLaunch l(grid, threads, 0, stream);
+    SaLaunch l(s, grid, threads, 0, stream);
     return cudaLaunchKernelEx(&l.cfg, sa_silu_mul_kernel, s, sides, (uint4*)out, (const uint4*)a, (const uint4*)b, scale);
+}
+
+// ---------------------------------------------------------------------------
+// cos/sin table of the rotary embedding
+// ---------------------------------------------------------------------------
+// table[t][i] = (cos(a), sin(a)) with a = (float)t * freq[i] rounded to fp32 as in
+// example_llmc_rope.cu:46-50.  Cosine and sine are taken in fp64 and rounded once, which is the
+// correctly rounded fp32 value except when the exact result lies within 2^-29 ulp of a rounding
+// boundary; libm's cosf/sinf are within 0.56 ulp, so the two agree to 1 ulp.  The table is a few
+// MiB and written once: a plain grid, no side awareness.
+namespace {
+struct SaRopeFreqs { float f[512]; };
+
+__global__ void sa_rope_table_kernel(float2* __restrict__ table, const __grid_constant__ SaRopeFreqs freqs, int half, long long entries) {
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < entries; e += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(e / half), i = (int)(e % half);
+        const float angle = __fmul_rn((float)t, freqs.f[i]);
+        double s, c;
+        sincos((double)angle, &s, &c);
+        table[e] = make_float2((float)c, (float)s);
+    }
+}
+} // namespace
+
+cudaError_t sa_launch_rope_table(float* table, const float* freqs, int half, int end, cudaStream_t stream) {
+    if (half <= 0 || half > 512 || end <= 0) return cudaErrorInvalidValue;
+    SaRopeFreqs f;
+    std::memset(&f, 0, sizeof(f));
+    std::memcpy(f.f, freqs, sizeof(float) * (size_t)half);
+    const long long entries = (long long)half * end;
+    long long blocks = (entries + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    sa_rope_table_kernel<<<(unsigned)blocks, 256, 0, stream>>>((float2*)table, f, half, entries);
+    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------

@@ -22,6 +22,8 @@ cudaError_t sa_launch_rope(const SaSched& s, const SaSideTable& sides, int grid,
                            const SaRopeShape& sh, bool bf16, cudaStream_t stream);
 cudaError_t sa_launch_silu_mul(const SaSched& s, const SaSideTable& sides, int grid, int threads, void* out, const void* a, const void* b,
                                float scale, cudaStream_t stream);
+// cos/sin table [end][half][2] from `half` frequencies (host memory, half <= 512)
+cudaError_t sa_launch_rope_table(float* table, const float* freqs, int half, int end, cudaStream_t stream);
 // Same kernel as sa_launch_memcpy with its ticket counters in a static device array (no allocation).
 cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int device, int grid, int threads, void* dst, const void* src,
                                      cudaStream_t stream);
@@ -35,8 +37,11 @@ int sa_memcpy_bulk_warps();
 // programmatic-stream-serialization attribute: when two of this library's kernels follow each other on a
 // stream, the second one's launch and prologue overlap the first one's tail; it touches data only after the
 // first has completed (griddepcontrol.wait in sa_for_each_chunk).  Measured: +3 % at 256 MiB, +1 % at 1 GiB.
+// Launches whose SaSched says overlap == 0 go without the attribute (every 32nd launch of a stream: that
+// bounds how many launches of a stream can be under way at once, see the ticket rings in sa_probe.cu).
+bool sa_pdl_enabled(); // false when SIDEAWARE_PDL=0
 struct SaLaunch {
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    SaLaunch(int grid, int threads, size_t smem, cudaStream_t stream);
+    SaLaunch(const SaSched& s, int grid, int threads, size_t smem, cudaStream_t stream);
 };

@@ -161,7 +161,7 @@ cudaError_t launch_cfg(const SaSched& s, const SaSideTable& sides, int grid, voi
         const char* e = std::getenv("SIDEAWARE_BULK_HINTS");
         return e ? std::atoi(e) & 3 : 0;
     }();
-    SaLaunch l(grid, WARPS * 32, smem, stream);
+    SaLaunch l(s, grid, WARPS * 32, smem, stream);
     return cudaLaunchKernelEx(&l.cfg, sa_memcpy_bulk_kernel<WARPS, S>, s, sides, (uint4*)dst, (const uint4*)src, hints);
 }
 

@@ -14,7 +14,9 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
+#include <unordered_map>
 
 #include "sa_probe.hpp"
 
@@ -26,8 +28,18 @@ constexpr int kDiscoverReps = 4;
 constexpr int kProbeReps = 3;
 constexpr int kVotes = 2;
 constexpr int kMaxBatch = 8192;     // addresses per probe launch
-constexpr int kTicketSlots = 256;
 constexpr int kTicketStride = 128;  // uint32 per slot (three counters on separate 128-byte lines)
+// Every stream has its own ring of ticket slots.  Launches of one stream run in order, so a slot
+// is free again once the launch that used it has ended.  A launch may begin while its predecessor
+// on the stream drains (programmatic dependent launch), and so may the one after it: what bounds
+// how many launches of a stream are under way at once is that every kChainLength-th launch waits
+// for its predecessor to END.  The ring is twice that long.  Launches of different streams never
+// share a slot, however long one of them runs.
+constexpr int kRingSlots = 64;
+constexpr int kChainLength = 32;
+constexpr int kRingsPerBlock = 64;  // rings carved from one 2 MiB device block
+constexpr int kMaxRings = 1024;     // distinct streams served before the rings are handed out afresh
+constexpr size_t kRingBlockBytes = sizeof(uint32_t) * kTicketStride * kRingSlots * kRingsPerBlock;
 constexpr uint32_t kSentinel = 0x9E3779B9u;
 
 __device__ __forceinline__ uint32_t atom_add_u32(uint32_t* p, uint32_t v) {
@@ -105,12 +117,18 @@ struct SaProbeDevice {
     uint32_t* seen = nullptr;     // [SA_MAX_SM]
     uint32_t* offsets = nullptr;  // [kNumAddr]
     unsigned char* gpu_side_index = nullptr; // [SA_MAX_SM]
-    uint32_t* tickets = nullptr;  // [kTicketSlots][kTicketStride]
+    uint32_t* tickets = nullptr;  // first block of rings: [kRingsPerBlock][kRingSlots][kTicketStride]
     uint64_t* addrs = nullptr;    // [kMaxBatch]
     uint32_t* out_lat = nullptr;  // [kVotes][kMaxBatch]
     uint16_t* out_smid = nullptr; // [kVotes][kMaxBatch]
-    unsigned next_slot = 0;
     std::mutex mu;
+    // ticket rings
+    struct Ring { uint32_t* base = nullptr; unsigned next = 0; };
+    std::mutex ring_mu;
+    std::unordered_map<void*, Ring*> ring_of_stream;
+    std::vector<std::unique_ptr<Ring>> rings;  // all rings ever carved
+    std::vector<Ring*> idle_rings;             // carved, not owned by a stream
+    std::vector<uint32_t*> ring_blocks;        // device blocks (the first one lives in `meta`)
 };
 
 static std::vector<uint32_t> make_offsets() {
@@ -143,7 +161,7 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
     size_t sz_seen = sizeof(uint32_t) * SA_MAX_SM;
     size_t sz_off = sizeof(uint32_t) * kNumAddr;
     size_t sz_side = SA_MAX_SM;
-    size_t sz_tick = sizeof(uint32_t) * kTicketSlots * kTicketStride;
+    size_t sz_tick = kRingBlockBytes;
     size_t sz_addr = sizeof(uint64_t) * kMaxBatch;
     size_t sz_olat = sizeof(uint32_t) * kVotes * kMaxBatch;
     size_t sz_osm = sizeof(uint16_t) * kVotes * kMaxBatch;
@@ -157,6 +175,7 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
     p->offsets = (uint32_t*)c; c += up(sz_off);
     p->gpu_side_index = c; c += up(sz_side);
     p->tickets = (uint32_t*)c; c += up(sz_tick);
+    p->ring_blocks.push_back(p->tickets);
     p->addrs = (uint64_t*)c; c += up(sz_addr);
     p->out_lat = (uint32_t*)c; c += up(sz_olat);
     p->out_smid = (uint16_t*)c; c += up(sz_osm);
@@ -206,25 +225,72 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
 
 void sa_probe_destroy(SaProbeDevice* p) {
     if (!p) return;
+    for (size_t i = 1; i < p->ring_blocks.size(); ++i) cudaFree(p->ring_blocks[i]);
     if (p->meta) cudaFree(p->meta);
     delete p;
 }
 
 unsigned char* sa_probe_gpu_side_index(SaProbeDevice* p) { return p->gpu_side_index; }
 
-uint32_t* sa_probe_ticket_slot(SaProbeDevice* p) {
-    unsigned s = __atomic_fetch_add(&p->next_slot, 1u, __ATOMIC_RELAXED) % kTicketSlots;
-    return p->tickets + (size_t)s * kTicketStride;
+// The ring of `stream`, made on first sight of the stream.  Called with ring_mu held.
+static SaProbeDevice::Ring* ring_for_stream(SaProbeDevice* p, void* stream) {
+    auto it = p->ring_of_stream.find(stream);
+    if (it != p->ring_of_stream.end()) return it->second;
+    if (p->idle_rings.empty()) {
+        if ((int)p->rings.size() >= kMaxRings) {
+            // More stream handles than rings (a program that keeps creating streams): once nothing
+            // is running on the device every ring is idle and can be handed out again.
+            if (cudaDeviceSynchronize() != cudaSuccess) return nullptr;
+            p->ring_of_stream.clear();
+            for (auto& r : p->rings) p->idle_rings.push_back(r.get());
+        } else {
+            // carve the next block (the first one came zeroed with the probe buffers)
+            size_t block = p->rings.size() / kRingsPerBlock;
+            if (block >= p->ring_blocks.size()) {
+                void* mem = nullptr;
+                if (cudaMalloc(&mem, kRingBlockBytes) != cudaSuccess) return nullptr;
+                if (cudaMemset(mem, 0, kRingBlockBytes) != cudaSuccess) { cudaFree(mem); return nullptr; }
+                p->ring_blocks.push_back((uint32_t*)mem);
+            }
+            for (int i = kRingsPerBlock - 1; i >= 0; --i) {
+                std::unique_ptr<SaProbeDevice::Ring> r(new SaProbeDevice::Ring());
+                r->base = p->ring_blocks[block] + (size_t)i * kRingSlots * kTicketStride;
+                p->idle_rings.push_back(r.get());
+                p->rings.push_back(std::move(r));
+            }
+        }
+    }
+    SaProbeDevice::Ring* r = p->idle_rings.back();
+    p->idle_rings.pop_back();
+    p->ring_of_stream.emplace(stream, r);
+    return r;
+}
+
+uint32_t* sa_probe_ticket_slot(SaProbeDevice* p, void* stream, bool* may_overlap_predecessor) {
+    std::lock_guard<std::mutex> lock(p->ring_mu);
+    SaProbeDevice::Ring* r = ring_for_stream(p, stream);
+    if (!r) return nullptr;
+    unsigned n = r->next++;
+    *may_overlap_predecessor = (n % kChainLength) != 0;
+    return r->base + (size_t)(n % kRingSlots) * kTicketStride;
 }
 
 unsigned long long sa_probe_wait_timeouts(SaProbeDevice* p) {
-    std::vector<uint32_t> words(kTicketSlots);
-    // word 96 of every slot: a strided copy of one uint32 per slot
-    if (cudaMemcpy2D(words.data(), sizeof(uint32_t), p->tickets + 96, sizeof(uint32_t) * kTicketStride, sizeof(uint32_t),
-                     kTicketSlots, cudaMemcpyDeviceToHost) != cudaSuccess)
-        return 0;
+    std::vector<uint32_t*> blocks;
+    {
+        std::lock_guard<std::mutex> lock(p->ring_mu);
+        blocks = p->ring_blocks;
+    }
+    const int slots = kRingSlots * kRingsPerBlock;
+    std::vector<uint32_t> words(slots);
     unsigned long long total = 0;
-    for (uint32_t w : words) total += w;
+    for (uint32_t* b : blocks) {
+        // word 96 of every slot: a strided copy of one uint32 per slot
+        if (cudaMemcpy2D(words.data(), sizeof(uint32_t), b + 96, sizeof(uint32_t) * kTicketStride, sizeof(uint32_t), slots,
+                         cudaMemcpyDeviceToHost) != cudaSuccess)
+            return total;
+        for (uint32_t w : words) total += w;
+    }
     return total;
 }
 

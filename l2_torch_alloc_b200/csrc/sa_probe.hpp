@@ -43,7 +43,10 @@ cudaError_t sa_probe_sides(SaProbeDevice* p, const SaTopology& topo, const uint6
 
 // Device pointers owned by the probe object.
 unsigned char* sa_probe_gpu_side_index(SaProbeDevice* p);
-uint32_t* sa_probe_ticket_slot(SaProbeDevice* p); // next free ticket slot (round robin)
+// Ticket slot for the next launch on `stream` (every stream has its own ring of slots), or nullptr if
+// a ring could not be made.  *may_overlap_predecessor is false for the launches that have to wait for
+// the end of their predecessor on the stream, so that the ring is never overrun.
+uint32_t* sa_probe_ticket_slot(SaProbeDevice* p, void* stream, bool* may_overlap_predecessor);
 // Sum of the error words of all ticket slots (bounded waits in kernels that ran out); synchronous.
 unsigned long long sa_probe_wait_timeouts(SaProbeDevice* p);
 

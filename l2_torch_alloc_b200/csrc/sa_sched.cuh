@@ -53,6 +53,7 @@ struct SaSched {
     sa_u32 active_warps;    // warps per block that take part (small arrays do not need all of them)
     sa_u32 share;           // tickets every active warp takes from its block's opening batch (no atomics)
     sa_u32 dynamic;         // 1: after the share, warps claim single tickets for themselves (large arrays)
+    sa_u32 overlap;         // host side only: 1 = the launch may begin while its predecessor on the stream drains
 };
 
 // Side of every SM (bit 0 of the byte), a kernel parameter of its own so that kernels which

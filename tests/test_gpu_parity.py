@@ -297,6 +297,81 @@ def test_rope_backward_matches_oracle(sa, shape, golden_dir):
     ch.cuda_free(tab)
 
 
+@pytest.mark.parametrize("case", [(64, 1024, 10000.0, 0), (64, 1024, 10000.0, 1), (128, 8192, 500000.0, 0),
+                                  (128, 8192, 500000.0, 1), (2, 5, 10000.0, 0), (48, 333, 1000000.0, 1)])
+def test_rope_table_made_on_the_gpu(sa, case, golden_dir):
+    """cos/sin table made on the GPU against precompute_freqs_cis (example_llmc_rope.cu:19-52, restated
+    in the oracle and, for the golden case, as written out by the compiled reference).  Tolerance: 1 fp32
+    ulp per entry (the task allows 1e-6 relative); the frequencies are bit-identical, the difference is
+    fp64 sincos rounded once on the GPU against libm's cosf/sinf (within 0.56 ulp), seen in ~1 % of entries."""
+    dim, end, theta, scaled = case
+    want = np.asarray(oracle.freqs_cis(dim, end, theta, scaled), dtype=np.float32).reshape(-1)
+    nbytes = want.nbytes
+    tab = ch.cuda_malloc(nbytes + 256)
+    ch.memset(tab, 0xEE, nbytes + 256)
+    sa.rope_precompute_freqs_ptr(tab, dim, end, theta, bool(scaled))
+    ch.sync()
+    raw = ch.d2h(tab, nbytes + 256)
+    ch.cuda_free(tab)
+    assert (raw[nbytes:] == 0xEE).all(), "wrote past the end of the table"
+    got = raw[:nbytes].view(np.float32)
+    ulps = np.abs(got.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64))
+    # +0 / -0 and values straddling zero do not occur: cos and sin of these angles are never that small
+    assert ulps.max() <= 1, f"max distance {ulps.max()} ulp"
+    if got.size >= 10000:
+        assert (ulps > 0).mean() <= 0.03
+    assert got[0] == 1.0 and got[1] == 0.0  # t = 0
+
+
+@pytest.mark.parametrize("scaled", [0, 1])
+def test_rope_table_against_golden_table_of_the_compiled_reference(sa, scaled, golden_dir):
+    g = np.load(os.path.join(golden_dir, "rope_small_f32.npz"))
+    want = g[f"table_s{scaled}"].astype(np.float32).reshape(-1)  # dim 8, 5 positions, theta 10000
+    tab = ch.cuda_malloc(want.nbytes)
+    sa.rope_precompute_freqs_ptr(tab, 8, 5, 10000.0, bool(scaled))
+    ch.sync()
+    got = ch.d2h(tab, want.nbytes).view(np.float32)
+    ch.cuda_free(tab)
+    assert np.abs(got.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64)).max() <= 1
+
+
+def test_rope_with_gpu_made_table_within_tolerance(sa):
+    """The whole path on the GPU (table, then rotation) against the reference's CPU path with its own table:
+    1e-6 relative to the magnitude of the pair, the tolerance the task states for fp32."""
+    B, T, Nq, Nkv, HS = 2, 256, 8, 2, 64
+    rng = np.random.default_rng(0xB200 + 7)
+    x = rng.uniform(-1, 1, size=(B, T, Nq + 2 * Nkv, HS)).astype(np.float32)
+    table = oracle.freqs_cis(HS, T, 10000.0, 0)
+    want = oracle.rope_forward_f32(x, table, B, T, Nq, Nkv, HS)
+    buf = ch.Guarded(sa, x.nbytes)
+    tab = ch.cuda_malloc(table.nbytes)
+    ch.h2d(buf.ptr, x)
+    sa.rope_precompute_freqs_ptr(tab, HS, T, 10000.0, False)
+    sa.rope_forward_ptr(buf.ptr, tab, B, T, Nq, Nkv, HS, False)
+    ch.sync()
+    got = ch.d2h(buf.ptr, x.nbytes).view(np.float32).reshape(x.shape)
+    assert buf.canaries_intact()
+    buf.free()
+    ch.cuda_free(tab)
+    pairs = x.reshape(B, T, -1, HS // 2, 2)
+    mag = np.sqrt((pairs.astype(np.float64) ** 2).sum(-1, keepdims=True)).repeat(2, -1).reshape(x.shape)
+    assert (np.abs(got.astype(np.float64) - want) <= 1e-6 * mag + 1e-12).all()
+    # V heads untouched
+    assert got[:, :, Nq + Nkv:].tobytes() == x[:, :, Nq + Nkv:].tobytes()
+
+
+def test_rope_table_rejects_bad_arguments(sa):
+    tab = ch.cuda_malloc(4096)
+    before = sa.error_count()
+    for dim, end, theta in [(0, 4, 1e4), (63, 4, 1e4), (2048, 4, 1e4), (64, 0, 1e4), (64, 4, 0.0)]:
+        with pytest.raises(RuntimeError):
+            sa.rope_precompute_freqs_ptr(tab, dim, end, theta, False)
+    with pytest.raises(RuntimeError):
+        sa.rope_precompute_freqs_ptr(0, 64, 4, 1e4, False)
+    assert sa.error_count() == before + 6
+    ch.cuda_free(tab)
+
+
 def test_rope_rejects_bad_shapes(sa):
     buf = sa.malloc(8 << 20)
     with pytest.raises(RuntimeError):
