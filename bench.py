@@ -200,6 +200,20 @@ def time_launches(torch, fn, steps, warmup, ranks=None, per_launch=False):
     return total, each
 
 
+def compiled_baseline(torch, fn, nbytes):
+    """fn() through torch.compile (inductor), as a comparison line only; the library itself uses no compiler of that kind."""
+    try:
+        t0 = time.perf_counter()
+        cfn = torch.compile(fn)
+        cfn()
+        torch.cuda.synchronize()
+        compile_s = time.perf_counter() - t0
+        ms, ea = time_launches(torch, cfn, 5, 2, None, per_launch=True)
+        return {"gbs": gbs(nbytes, statistics.mean(ea)), "ms": statistics.mean(ea), "compile_s": compile_s}
+    except Exception as exc:  # no compiler on the box, unsupported construct ...: the baseline is optional
+        return {"unavailable": repr(exc)[:200]}
+
+
 def load_cudart(torch):
     """The CUDA runtime torch already loaded, for cudaMemcpyAsync on raw pointers."""
     import ctypes
@@ -610,6 +624,9 @@ def run_ours(args, ranks):
         rope[mode] = {"gbs": gbs(rope_bytes_moved, statistics.mean(ea)), "best_gbs": gbs(rope_bytes_moved, min(ea)),
                       "ms": statistics.mean(ea)}
     sa.set_placement("aware")
+    if ranks.rank == 0:  # the same launches with no event between them, as the headline is timed
+        tot, _ = time_launches(torch, rope_step, rope_steps, 3, None, per_launch=False)
+        rope["aware"]["back_to_back_gbs"] = gbs(rope_bytes_moved, tot / rope_steps)
     rope["algorithmic_bytes"] = rope_bytes_moved
     rope["frac_of_peak"] = rope["aware"]["gbs"] / peak
     rope["config"] = "bf16 B=8 T=8192 32q+8kv HS=128 theta=500000 in place"
@@ -629,6 +646,8 @@ def run_ours(args, ranks):
 
         ms, ea = time_launches(torch, eager_rope, 5, 2, None, per_launch=True)
         rope["torch_eager"] = {"gbs": gbs(rope_bytes_moved, statistics.mean(ea)), "ms": statistics.mean(ea)}
+        if ranks.world == 1 and not args.no_torch_compile:
+            rope["torch_compile"] = compiled_baseline(torch, eager_rope, rope_bytes_moved)
         del xt, cos, sin
     del x, table
 
@@ -656,6 +675,9 @@ def run_ours(args, ranks):
                 ms, ea = time_launches(torch, f, 10, 2, None, per_launch=True)
                 functor[f"{name}_{mode}"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea)}
         sa.set_placement("aware")
+        for name, f in (("aot", f_aot), ("nvrtc", f_jit)):
+            tot, _ = time_launches(torch, f, 10, 2, None, per_launch=False)
+            functor[f"{name}_aware"]["back_to_back_gbs"] = gbs(6 * n, tot / 10)
         functor["frac_of_peak"] = functor["aot_aware"]["gbs"] / peak
         for buf in (a, b, o):
             lib.sideaware_free_auto(buf, 2 * n, dev, sp)
@@ -667,6 +689,8 @@ def run_ours(args, ranks):
         ms, ea = time_launches(torch, lambda: torch.nn.functional.silu(ta) * tb * 0.5, 5, 2, None, per_launch=True)
         functor["torch_eager"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea),
                                   "note": "three kernels with bf16 temporaries; GB/s counts the same 6 bytes per element"}
+        if ranks.world == 1 and not args.no_torch_compile:
+            functor["torch_compile"] = compiled_baseline(torch, lambda: torch.nn.functional.silu(ta) * tb * 0.5, 6 * n)
         del ta, tb
         if sa.error_count():
             functor["errors"] = sa.last_error()
@@ -713,6 +737,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-torch-compile", action="store_true", help="skip the torch.compile comparison lines")
     ap.add_argument("--churn-ops", type=int, default=5000,
                     help="allocator churn operations (N = 1 only; 0 = skip; the full configuration is 10000)")
     ap.add_argument("--power-seconds", type=float, default=2.0, help="length of each power sampling loop (0 = skip)")
