@@ -178,6 +178,8 @@ typedef struct sideaware_stats_t {
     unsigned long long probe_confidence_ppm; /* min SM signature margin, 1e6 = perfect */
     unsigned long long hash_validation_errors; /* mispredicted validation offsets at init */
     unsigned long long kernel_wait_timeouts;   /* bounded waits inside kernels that ran out (0 in a healthy run) */
+    unsigned long long handles_created;        /* cuMemCreate calls; pages_created counts the 2 MiB pages they hold */
+    unsigned long long handles_discarded;      /* handles given back because their pages' sides did not alternate */
 } sideaware_stats_t;
 void sideaware_get_stats(sideaware_stats_t* out);
 

@@ -10,21 +10,66 @@ static inline size_t round_to_pages(size_t size) {
 
 static inline int side_bit(uint64_t va) { return (int)((va >> kSaSideBit) & 1); }
 
+// Pages created between two measurements.  Guesses about a chunk build on guesses about the
+// chunks before it, so with chunks a round is two groups long: one boundary that does not behave
+// as expected then costs one group, not many.  Single pages are judged one by one, and a long
+// round saves probe launches.
+constexpr int kChunkRound = 2 * kSaGroupPages;
+constexpr int kSinglesRound = 64;
+
 SaAllocator::~SaAllocator() {
     // Process teardown: the driver reclaims everything; touching it here could run
     // after the CUDA context is gone.
 }
 
 // ---------------------------------------------------------------------------
-// physical pages
+// physical memory not mapped anywhere
 // ---------------------------------------------------------------------------
 
 void SaAllocator::release_pools() {
     for (int c = 0; c < 2; ++c)
-        for (int s = 0; s < 2; ++s) {
-            for (auto& pg : pool_[c][s]) be_->release_page(pg.handle);
-            pool_[c][s].clear();
-        }
+        for (int s = 0; s < 2; ++s)
+            for (int l = 1; l <= kSaMaxChunkPages; ++l) {
+                for (auto& ch : pool_[c][s][l]) be_->release_chunk(ch.handle);
+                pool_[c][s][l].clear();
+            }
+}
+
+void SaAllocator::pool_push(bool compressed, const Chunk& c) {
+    if (c.side > 1 || c.len < 1 || c.len > kSaMaxChunkPages) { // never measured: nothing is known about it
+        be_->release_chunk(c.handle);
+        return;
+    }
+    pool_[compressed][c.side][c.len].push_back(c);
+}
+
+bool SaAllocator::pool_pop(bool compressed, int side, int len, Chunk* out) {
+    auto& v = pool_[compressed][side][len];
+    if (v.empty()) return false;
+    *out = v.back();
+    v.pop_back();
+    return true;
+}
+
+// pooled pages homed on `side` (a chunk's pages alternate from the side of its page 0)
+size_t SaAllocator::pooled_pages(bool compressed, int side) const {
+    size_t n = 0;
+    for (int s = 0; s < 2; ++s)
+        for (int l = 1; l <= kSaMaxChunkPages; ++l)
+            n += pool_[compressed][s][l].size() * (size_t)(s == side ? (l + 1) / 2 : l / 2);
+    return n;
+}
+
+// Keeps the guess about the physical layout up to date: `sides` are those of newly created
+// pages in the order they were created.  Inside a group sides alternate; a side seen twice in a
+// row marks a group boundary just before the second one.
+void SaAllocator::note_fresh_sides(const uint8_t* sides, int n) {
+    for (int i = 0; i < n; ++i) {
+        const int x = sides[i] & 1;
+        if (phys_last_side_ >= 0 && x == phys_last_side_) phys_pos_ = 0;
+        phys_pos_ = (phys_pos_ + 1) % kSaGroupPages;
+        phys_last_side_ = x;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -118,17 +163,17 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
 // Maps a new segment of exactly `pages` pages whose first page is on side `phase` and hands all
 // of it out as one block.
 //
-// Pages come from the per-side pools where they can.  The rest is created fresh and mapped
-// STRAIGHT INTO PLACE: only then can a page's side be measured, and about half of the fresh pages
-// turn out to sit in a slot of the right side already.  Misplaced ones are exchanged pairwise (a
-// side-1 page in a side-0 slot with a side-0 page in a side-1 slot); what cannot be paired goes
-// to the pool of its true side and its slot is filled in the next round.  The reference probes
-// every new page through a temporary mapping first (sideaware.cu:947-1019), which on B200 costs
-// one more cuMemSetAccess (~170 us) and cuMemUnmap (~90 us) per page than this does for the half
-// that lands well.
+// 1) Pooled chunks (their sides are known) are put where they fit, largest first.
+// 2) The rest is created fresh, a few chunks per round, each mapped where the pages seen so far
+//    suggest it will fit, then measured IN PLACE (only a mapped page can be measured): a chunk that
+//    fits stays, one that alternates but starts on the other side is moved to a place that wants it
+//    or pooled, one whose pages do not alternate is given back and re-made in two pieces split
+//    where the side repeated.  The reference probes every new page through a temporary mapping
+//    first (sideaware.cu:947-1019), at one more cuMemSetAccess and cuMemUnmap per page.
+// 3) If device memory ran out on the way, pooled chunks of the other side fill what is left
+//    (slower, still correct).
 uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg) {
     (void)cfg;
-    auto& pools = pool_[compressed];
     std::unique_ptr<Segment> seg(new Segment());
     seg->compressed = compressed;
     seg->num_pages = pages;
@@ -137,120 +182,269 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
     seg->base = seg->reserved;
     if (side_bit(seg->base) != phase) seg->base += kSaPageBytes;
-    seg->pages.assign(pages, Page{0, 0});
+    seg->pages.assign(pages, Slot{});
+    std::vector<Slot>& slots = seg->pages;
     auto slot_va = [&](size_t i) { return seg->base + i * kSaPageBytes; };
+    auto want = [&](size_t i) { return side_bit(slot_va(i)); };
 
     bool ok = true;
-    std::vector<size_t> missing; // slots without a page yet
-    // 1) pooled pages of the matching side
-    for (size_t i = 0; i < pages && ok; ++i) {
-        const int want = side_bit(slot_va(i));
-        if (pools[want].empty()) { missing.push_back(i); continue; }
-        Page pg = pools[want].back();
-        pools[want].pop_back();
-        if (be_->map_page(slot_va(i), pg.handle)) {
-            pools[pg.side].push_back(pg);
-            ok = false;
-            break;
+    size_t empty = pages;
+    size_t first_empty = 0;
+
+    // maps chunk `c` at slot `at`; a chunk that cannot be mapped goes back to the pool (or the driver)
+    auto put = [&](size_t at, const Chunk& c) -> bool {
+        if (be_->map_chunk(slot_va(at), c.handle, c.len)) {
+            pool_push(compressed, c);
+            return false;
         }
-        seg->pages[i] = pg;
-    }
-    // access for what is mapped so far, in contiguous pieces (a range with holes cannot be opened at once)
-    auto open_ranges = [&](const std::vector<size_t>& slots) -> bool { // slots ascending
-        size_t k = 0;
-        while (k < slots.size()) {
-            size_t e = k;
-            while (e + 1 < slots.size() && slots[e + 1] == slots[e] + 1) ++e;
-            if (be_->set_access(slot_va(slots[k]), (e - k + 1) * kSaPageBytes)) return false;
-            k = e + 1;
+        for (int k = 0; k < c.len; ++k) {
+            Slot& sl = slots[at + k];
+            sl.handle = c.handle;
+            sl.len = c.len;
+            sl.idx = (uint8_t)k;
+            sl.side = c.side <= 1 ? (uint8_t)(c.side ^ (k & 1)) : (uint8_t)2;
         }
+        empty -= c.len;
         return true;
     };
-    if (ok) {
-        std::vector<size_t> pooled;
-        for (size_t i = 0; i < pages; ++i)
-            if (seg->pages[i].handle) pooled.push_back(i);
-        ok = open_ranges(pooled);
+    // unmaps the chunk that starts at slot `at`
+    auto lift = [&](size_t at) -> Chunk {
+        Chunk c;
+        c.handle = slots[at].handle;
+        c.len = slots[at].len;
+        c.side = slots[at].side;
+        be_->unmap_chunk(slot_va(at), c.len);
+        for (int k = 0; k < c.len; ++k) slots[at + k] = Slot{};
+        empty += c.len;
+        if (at < first_empty) first_empty = at;
+        return c;
+    };
+    // access for newly mapped chunks, one call per contiguous stretch
+    auto open = [&](std::vector<std::pair<size_t, int>>& placed) -> bool { // (slot, len)
+        std::sort(placed.begin(), placed.end());
+        size_t k = 0;
+        while (k < placed.size()) {
+            size_t from = placed[k].first, to = from + placed[k].second;
+            while (k + 1 < placed.size() && placed[k + 1].first == to) to += placed[++k].second;
+            if (be_->set_access(slot_va(from), (to - from) * kSaPageBytes)) return false;
+            ++k;
+        }
+        placed.clear();
+        return true;
+    };
+    // leftmost place where `len` empty slots start with one that wants side `s`: the start of an
+    // empty stretch, or its second slot (the first is then left for a single page)
+    auto find_place = [&](int len, int s, size_t* at) -> bool {
+        while (first_empty < pages && slots[first_empty].handle) ++first_empty;
+        size_t i = first_empty;
+        while (i < pages) {
+            if (slots[i].handle) { ++i; continue; }
+            const size_t cand = want(i) == s ? i : i + 1;
+            size_t e = i;
+            while (e < pages && e < cand + len && !slots[e].handle) ++e;
+            if (e >= cand + len) { *at = cand; return true; }
+            while (e < pages && !slots[e].handle) ++e; // too short: skip the rest of this stretch
+            i = e;
+        }
+        return false;
+    };
+    auto largest_room = [&](int cap) -> int { // longest empty stretch, counted up to `cap`
+        int best = 0;
+        size_t i = first_empty;
+        while (i < pages && best < cap) {
+            if (slots[i].handle) { ++i; continue; }
+            int run = 0;
+            while (i < pages && !slots[i].handle) { ++i; if (++run >= cap) break; }
+            best = std::max(best, run);
+        }
+        return best;
+    };
+
+    std::vector<std::pair<size_t, int>> placed;
+    // 1) pooled chunks, exactly where they fit
+    {
+        size_t i = 0;
+        while (ok && i < pages) {
+            const int room = (int)std::min<size_t>(pages - i, kSaMaxChunkPages);
+            const int w = want(i);
+            Chunk c;
+            bool found = false;
+            for (int l = room; l >= 1 && !found; --l) found = pool_pop(compressed, w, l, &c);
+            if (!found) { ++i; continue; }
+            if (!put(i, c)) { ok = false; break; }
+            placed.emplace_back(i, c.len);
+            i += c.len;
+        }
+        if (ok) ok = open(placed);
     }
-    // 2) fresh pages, probed where they are
+
+    // 2) fresh chunks, measured where they are mapped
+    struct Fresh { size_t at; int len; bool remade; };
+    std::vector<Fresh> fresh;
     std::vector<uint64_t> vas;
     std::vector<uint8_t> sides;
-    for (int round = 0; ok && !missing.empty() && round < 48; ++round) { // leftovers halve every round
-        std::vector<size_t> fresh;
-        for (size_t i : missing) {
+    std::vector<Chunk> displaced;
+    bool memory_left = true;
+    const int max_rounds = 64 + (int)(pages / 4);
+    auto leftmost = [&](int len, size_t* at) -> bool {
+        size_t a0 = 0, a1 = 0;
+        const bool h0 = find_place(len, 0, &a0), h1 = find_place(len, 1, &a1);
+        if (!h0 && !h1) return false;
+        *at = (h0 && (!h1 || a0 <= a1)) ? a0 : a1;
+        return true;
+    };
+    for (int round = 0; ok && empty > 0 && memory_left && round < max_rounds; ++round) {
+        fresh.clear();
+        // what the pages about to be created are expected to look like
+        int pred_pos = phys_pos_, pred_last = phys_last_side_;
+        const size_t budget = std::min<size_t>(empty, (size_t)(singles_left_ > 0 ? kSinglesRound : round_pages_));
+        size_t planned = 0;
+        while (ok && planned < budget) {
+            // size: never across the expected group boundary; 7 at the start of a group, so that the
+            // group's last page comes as a single and the eight can be laid down either way round
+            int len, s_hat;
+            const bool remade = !forced_.empty();
+            if (remade) {
+                len = forced_.back().first;
+                s_hat = forced_.back().second;
+            } else {
+                len = singles_left_ > 0 ? 1 : (pred_pos == 0 ? kSaMaxChunkPages : kSaGroupPages - pred_pos);
+                s_hat = pred_last < 0 ? -1 : (pred_pos == 0 ? pred_last : pred_last ^ 1);
+            }
+            len = std::min<int>(len, (int)std::min<size_t>(budget - planned, kSaMaxChunkPages));
+            len = std::min(len, largest_room(len));
+            if (len < 1) break;
+            size_t at = 0;
+            if (s_hat < 0 || !find_place(len, s_hat, &at)) {
+                // no expectation, or no room where that side is wanted: one page shorter fits one slot further on
+                if (s_hat >= 0 && len > 1 && find_place(len - 1, s_hat, &at)) len -= 1;
+                else if (!leftmost(len, &at)) break;
+            }
             uint64_t h = 0;
-            if (be_->create_page(&h, compressed)) break; // device memory exhausted: step 3 decides
-            if (be_->map_page(slot_va(i), h)) { be_->release_page(h); ok = false; break; }
-            seg->pages[i] = Page{h, 2}; // side unknown
-            fresh.push_back(i);
-            st_.pages_created++;
+            if (be_->create_chunk(&h, len, compressed)) {
+                forced_.clear();
+                if (len > 1) { singles_left_ = 64; continue; } // no piece of that size left: single pages may still be had
+                memory_left = false;
+                break;
+            }
+            st_.handles_created++;
+            st_.pages_created += (uint64_t)len;
+            if (remade) forced_.pop_back();
+            else if (singles_left_ > 0) --singles_left_;
+            Chunk c;
+            c.handle = h;
+            c.len = (uint8_t)len;
+            c.side = 2;
+            if (!put(at, c)) { ok = false; break; }
+            placed.emplace_back(at, len);
+            fresh.push_back(Fresh{at, len, remade});
+            planned += (size_t)len;
+            if (!remade) {
+                const int first = s_hat >= 0 ? s_hat : want(at);
+                pred_last = first ^ ((len - 1) & 1);
+                pred_pos = (pred_pos + len) % kSaGroupPages;
+            }
         }
         if (!ok || fresh.empty()) break;
-        if (!open_ranges(fresh)) { ok = false; break; }
+        if (!open(placed)) { ok = false; break; }
         vas.clear();
-        for (size_t i : fresh) vas.push_back(slot_va(i));
-        sides.assign(fresh.size(), 0);
-        if (be_->probe_pages(vas.data(), (int)fresh.size(), sides.data(), stream)) { ok = false; break; }
-        std::vector<size_t> wrong[2]; // wrong[w]: slots that want side w and hold a page of side 1 - w
-        for (size_t k = 0; k < fresh.size(); ++k) {
-            const size_t i = fresh[k];
-            seg->pages[i].side = sides[k] & 1;
-            const int want = side_bit(slot_va(i));
-            if ((int)seg->pages[i].side != want) wrong[want].push_back(i);
-        }
-        // exchange misplaced pages pairwise
-        while (ok && !wrong[0].empty() && !wrong[1].empty()) {
-            const size_t i = wrong[0].back(), j = wrong[1].back();
-            wrong[0].pop_back();
-            wrong[1].pop_back();
-            be_->unmap_page(slot_va(i));
-            be_->unmap_page(slot_va(j));
-            std::swap(seg->pages[i], seg->pages[j]);
-            if (be_->map_page(slot_va(i), seg->pages[i].handle)) { pools[seg->pages[i].side].push_back(seg->pages[i]); seg->pages[i] = Page{0, 0}; ok = false; }
-            if (be_->map_page(slot_va(j), seg->pages[j].handle)) { pools[seg->pages[j].side].push_back(seg->pages[j]); seg->pages[j] = Page{0, 0}; ok = false; }
-            if (ok && (be_->set_access(slot_va(i), kSaPageBytes) || be_->set_access(slot_va(j), kSaPageBytes))) ok = false;
-        }
-        // what is left over is all of one kind: those pages wait in the pool of their true side
-        std::vector<size_t> still;
-        for (int w = 0; w < 2; ++w)
-            for (size_t i : wrong[w]) {
-                be_->unmap_page(slot_va(i));
-                pools[seg->pages[i].side].push_back(seg->pages[i]);
-                seg->pages[i] = Page{0, 0};
-                still.push_back(i);
+        for (auto& f : fresh)
+            for (int k = 0; k < f.len; ++k) vas.push_back(slot_va(f.at + (size_t)k));
+        sides.assign(vas.size(), 0);
+        if (be_->probe_pages(vas.data(), (int)vas.size(), sides.data(), stream)) { ok = false; break; }
+        // judge them in the order they were created
+        displaced.clear();
+        size_t off = 0;
+        int bad = 0;
+        for (auto& f : fresh) {
+            const uint8_t* sd = &sides[off];
+            off += (size_t)f.len;
+            if (!f.remade) note_fresh_sides(sd, f.len); // a re-made piece lies behind what came after it: it says nothing new
+            int rep = 0; // first page on the same side as the page before it
+            for (int k = 1; k < f.len && !rep; ++k)
+                if ((sd[k] & 1) == (sd[k - 1] & 1)) rep = k;
+            if (rep) {
+                // Unusable as a whole.  The driver hands freed memory out again first, so the same pages
+                // can be had as two chunks that end and begin at the boundary just found.
+                Chunk c = lift(f.at);
+                be_->release_chunk(c.handle);
+                st_.handles_discarded++;
+                ++bad;
+                if (!f.remade) {
+                    forced_.emplace_back(f.len - rep, sd[rep] & 1);
+                    forced_.emplace_back(rep, sd[0] & 1); // taken from the back: this one first
+                }
+                continue;
             }
-        // slots for which no page could be created stay missing too
-        for (size_t i : missing)
-            if (!seg->pages[i].handle && std::find(still.begin(), still.end(), i) == still.end()) still.push_back(i);
-        std::sort(still.begin(), still.end());
-        missing.swap(still);
+            const int s0 = sd[0] & 1;
+            if (s0 == want(f.at)) {
+                for (int k = 0; k < f.len; ++k) slots[f.at + (size_t)k].side = (uint8_t)(s0 ^ (k & 1));
+                continue;
+            }
+            Chunk c = lift(f.at);
+            c.side = (uint8_t)s0;
+            displaced.push_back(c);
+        }
+        // what did not fit where it was put: its sides are known now, so place it exactly, largest first
+        const size_t moved = displaced.size();
+        std::sort(displaced.begin(), displaced.end(), [](const Chunk& a, const Chunk& b) { return a.len > b.len; });
+        for (auto& c : displaced) {
+            size_t at = 0;
+            if (ok && find_place(c.len, c.side, &at)) {
+                if (!put(at, c)) { ok = false; continue; }
+                placed.emplace_back(at, (int)c.len);
+            } else {
+                pool_push(compressed, c);
+            }
+        }
+        if (ok && !placed.empty()) ok = open(placed);
+        // longer rounds while the guesses hold, short ones and finally single pages while they do not
+        if (bad) {
+            round_pages_ = kSaGroupPages;
+            recent_bad_ += bad;
+            if (recent_bad_ >= 3) {
+                // physical memory is not laid out as hoped (fragmented by earlier use): single pages for a
+                // while, for twice as long every time chunks fail again
+                singles_left_ = singles_span_;
+                singles_span_ = std::min(singles_span_ * 2, 8192);
+                forced_.clear();
+                recent_bad_ = 0;
+            }
+        } else {
+            if (recent_bad_ > 0) --recent_bad_;
+            if (moved * 4 <= fresh.size()) round_pages_ = std::min(kChunkRound, round_pages_ * 2);
+            if (singles_left_ == 0 && fresh.size() >= 2 && fresh[0].len > 1) singles_span_ = 64; // chunks work again
+        }
     }
-    // 3) no page of the right side to be had: one of the other side still works, only slower
-    if (ok && !missing.empty()) {
-        std::vector<size_t> crossed;
-        for (size_t i : missing) {
-            const int other = side_bit(slot_va(i)) ^ 1;
-            if (pools[other].empty()) { ok = false; break; }
-            if (!warned_cross_) {
-                std::fprintf(stderr, "sideaware: no free page on side %d, mapping a page of the other side (slower, still correct)\n", other ^ 1);
+    // 3) device memory ran out: whatever is pooled fills the rest, whichever side it is on
+    if (ok && empty > 0) {
+        size_t i = 0;
+        while (ok && i < pages) {
+            if (slots[i].handle) { ++i; continue; }
+            int room = 0;
+            while (i + (size_t)room < pages && room < kSaMaxChunkPages && !slots[i + (size_t)room].handle) ++room;
+            Chunk c;
+            bool found = false;
+            for (int l = room; l >= 1 && !found; --l)
+                for (int s = 0; s < 2 && !found; ++s) found = pool_pop(compressed, want(i) ^ s, l, &c);
+            if (!found) { ok = false; break; }
+            if (!put(i, c)) { ok = false; break; }
+            placed.emplace_back(i, (int)c.len);
+            for (int k = 0; k < c.len; ++k)
+                if ((int)slots[i + (size_t)k].side != want(i + (size_t)k)) st_.cross_side_pages++;
+            if (c.side != want(i) && !warned_cross_) {
+                std::fprintf(stderr, "sideaware: device memory is short, mapping pages against their side (slower, still correct)\n");
                 warned_cross_ = true;
             }
-            Page pg = pools[other].back();
-            pools[other].pop_back();
-            if (be_->map_page(slot_va(i), pg.handle)) { pools[pg.side].push_back(pg); ok = false; break; }
-            seg->pages[i] = pg;
-            st_.cross_side_pages++;
-            crossed.push_back(i);
+            i += c.len;
         }
-        if (ok) ok = open_ranges(crossed);
+        if (ok) ok = open(placed);
     }
     if (!ok) {
         for (size_t i = 0; i < pages; ++i) {
-            Page& pg = seg->pages[i];
-            if (!pg.handle) continue;
-            be_->unmap_page(slot_va(i));
-            if (pg.side <= 1) pools[pg.side].push_back(pg);
-            else be_->release_page(pg.handle); // never measured: give it back
+            if (!slots[i].handle || slots[i].idx != 0) continue;
+            Chunk c = lift(i);
+            pool_push(compressed, c); // a chunk that was never measured goes back to the driver
         }
         be_->free_va(seg->reserved, seg->reserved_bytes);
         return 0;
@@ -267,23 +461,48 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     return base;
 }
 
-// Unmaps the pages of a free run (already removed from the free indices) and returns them to
-// the pools.  The hole stays reserved until the whole segment is unmapped.
+// Unmaps what can be unmapped of a free run (already removed from the free indices) and returns
+// it to the pools.  A mapping can only be undone as a whole, so pages of chunks that reach beyond
+// the run stay mapped and go back into the free indices.  Holes stay reserved until the whole
+// segment is unmapped.
 void SaAllocator::unmap_run(uint64_t va, const Run& run) {
     Segment* seg = run.seg;
-    const size_t first = (size_t)((va - seg->base) / kSaPageBytes);
-    for (size_t i = 0; i < run.pages; ++i) {
-        Page& pg = seg->pages[first + i];
-        be_->unmap_page(va + i * kSaPageBytes);
-        pool_[seg->compressed][pg.side].push_back(pg);
-        pg.handle = 0;
+    const size_t first = (size_t)((va - seg->base) / kSaPageBytes), last = first + run.pages;
+    const size_t none = (size_t)-1;
+    size_t kept_from = none;
+    auto keep_until = [&](size_t end) {
+        if (kept_from == none) return;
+        Run rest = run;
+        rest.pages = end - kept_from;
+        insert_free(seg->base + kept_from * kSaPageBytes, rest);
+        kept_from = none;
+    };
+    size_t i = first;
+    while (i < last) {
+        const Slot sl = seg->pages[i];
+        const size_t c0 = i - sl.idx, c1 = c0 + sl.len; // slots of the chunk this page belongs to
+        if (c0 >= first && c1 <= last) {
+            keep_until(i);
+            be_->unmap_chunk(seg->base + c0 * kSaPageBytes, sl.len);
+            Chunk c;
+            c.handle = sl.handle;
+            c.len = sl.len;
+            c.side = seg->pages[c0].side;
+            pool_push(seg->compressed, c);
+            for (size_t k = c0; k < c1; ++k) seg->pages[k] = Slot{};
+            seg->mapped_pages -= sl.len;
+            i = c1;
+        } else {
+            if (kept_from == none) kept_from = i;
+            i = std::min(c1, last);
+        }
     }
-    seg->mapped_pages -= run.pages;
+    keep_until(last);
     if (seg->mapped_pages == 0) {
         be_->free_va(seg->reserved, seg->reserved_bytes);
-        for (size_t i = 0; i < segments_.size(); ++i)
-            if (segments_[i].get() == seg) {
-                segments_[i] = std::move(segments_.back());
+        for (size_t k = 0; k < segments_.size(); ++k)
+            if (segments_[k].get() == seg) {
+                segments_[k] = std::move(segments_.back());
                 segments_.pop_back();
                 break;
             }
@@ -324,7 +543,7 @@ int SaAllocator::choose_phase(size_t bytes, size_t pages, bool compressed) {
     int phase;
     auto fit = free_by_len_[compressed].lower_bound(pages);
     if (fit != free_by_len_[compressed].end()) phase = side_bit(fit->second);
-    else phase = pool_[compressed][0].size() >= pool_[compressed][1].size() ? 0 : 1;
+    else phase = pooled_pages(compressed, 0) >= pooled_pages(compressed, 1) ? 0 : 1;
     phase_.emplace(bytes, phase);
     return phase;
 }
@@ -399,7 +618,7 @@ size_t SaAllocator::release_unused() {
     trim_locked(0, 0);
     size_t released = 0;
     for (int c = 0; c < 2; ++c)
-        for (int s = 0; s < 2; ++s) released += pool_[c][s].size() * kSaPageBytes;
+        for (int s = 0; s < 2; ++s) released += pooled_pages(c != 0, s) * kSaPageBytes;
     release_pools();
     be_->device_sync();
     return released;
@@ -410,8 +629,8 @@ SaAllocStats SaAllocator::stats() {
     SaAllocStats s = st_;
     s.bytes_live = live_bytes_;
     s.bytes_cached = cached_bytes_;
-    s.pages_pool[0] = pool_[0][0].size() + pool_[1][0].size();
-    s.pages_pool[1] = pool_[0][1].size() + pool_[1][1].size();
+    s.pages_pool[0] = pooled_pages(false, 0) + pooled_pages(true, 0);
+    s.pages_pool[1] = pooled_pages(false, 1) + pooled_pages(true, 1);
     s.segments = segments_.size();
     s.free_runs = free_.size();
     return s;

@@ -459,6 +459,8 @@ SA_API void sideaware_get_stats(sideaware_stats_t* out) {
     out->large_allocs = st.large_allocs;
     out->small_allocs = dev->small_allocs.load();
     out->trims = st.trims;
+    out->handles_created = st.handles_created;
+    out->handles_discarded = st.handles_discarded;
     out->jit_compiles = dev->jit_compiles.load();
     out->kernel_launches = dev->launches.load();
     out->probe_confidence_ppm = (unsigned long long)(dev->topo.confidence > 0 ? dev->topo.confidence * 1e6 : 0);

@@ -72,7 +72,7 @@ class CudaBackend : public SaBackend {
 public:
     explicit CudaBackend(SaDevice* dev) : dev_(dev), d_(dev->drv) {}
 
-    int create_page(uint64_t* handle, bool compressed) override {
+    int create_chunk(uint64_t* handle, int pages, bool compressed) override {
         ScopedTime st(T_CREATE);
         CUmemAllocationProp prop;
         std::memset(&prop, 0, sizeof(prop));
@@ -81,11 +81,11 @@ public:
         prop.location.id = dev_->id;
         prop.allocFlags.compressionType = compressed ? CU_MEM_ALLOCATION_COMP_GENERIC : 0;
         CUmemGenericAllocationHandle h = 0;
-        CUresult r = d_->MemCreate(&h, kSaPageBytes, &prop, 0);
+        CUresult r = d_->MemCreate(&h, (size_t)pages * kSaPageBytes, &prop, 0);
         *handle = (uint64_t)h;
         return (int)r;
     }
-    void release_page(uint64_t handle) override {
+    void release_chunk(uint64_t handle) override {
         ScopedTime st(T_RELEASE);
         d_->MemRelease((CUmemGenericAllocationHandle)handle);
     }
@@ -100,13 +100,13 @@ public:
         ScopedTime st(T_RESERVE);
         d_->MemAddressFree((CUdeviceptr)va, bytes);
     }
-    int map_page(uint64_t va, uint64_t handle) override {
+    int map_chunk(uint64_t va, uint64_t handle, int pages) override {
         ScopedTime st(T_MAP);
-        return (int)d_->MemMap((CUdeviceptr)va, kSaPageBytes, 0, (CUmemGenericAllocationHandle)handle, 0);
+        return (int)d_->MemMap((CUdeviceptr)va, (size_t)pages * kSaPageBytes, 0, (CUmemGenericAllocationHandle)handle, 0);
     }
-    void unmap_page(uint64_t va) override {
+    void unmap_chunk(uint64_t va, int pages) override {
         ScopedTime st(T_UNMAP);
-        d_->MemUnmap((CUdeviceptr)va, kSaPageBytes);
+        d_->MemUnmap((CUdeviceptr)va, (size_t)pages * kSaPageBytes);
     }
     int set_access(uint64_t va, size_t bytes) override {
         ScopedTime st(T_ACCESS);

@@ -126,34 +126,78 @@ static void test_sched() {
 // ---------------------------------------------------------------------------
 // allocator on a simulated driver
 // ---------------------------------------------------------------------------
+// Simulated driver.  Physical memory is a line of 2 MiB pages handed out in order (memory that
+// was released is handed out again first, most recently released first).  Sides of consecutive
+// pages follow one of three models:
+//   0  what was measured on B200: alternating inside groups of 8 pages; at most group boundaries
+//      the side repeats once
+//   1  independent random sides (bias_percent = chance of side 1)
+//   2  model 0 with the line starting inside a group (a process that created pages before)
 struct FakeDriver : SaBackend {
+    static int default_model;
+    int model = default_model;
     uint64_t next_handle = 1, next_va = 0x7f0000000000ull;
     size_t capacity_pages = 1 << 20;
-    std::map<uint64_t, int> page_side;       // live handles -> true side
-    std::map<uint64_t, size_t> reservations; // va -> bytes
-    std::map<uint64_t, uint64_t> mappings;   // va -> handle
+    size_t next_phys = 0;
+    std::vector<std::pair<size_t, size_t>> holes;            // released physical ranges (start, pages), newest last
+    std::map<size_t, int> random_side;                        // model 1: side of a physical page once drawn
+    struct Handle { size_t phys; int pages; };
+    std::map<uint64_t, Handle> handles;                       // live handles
+    std::map<uint64_t, size_t> reservations;                  // va -> bytes
+    std::map<uint64_t, std::pair<uint64_t, int>> mappings;    // page va -> (handle, page of the handle)
     std::set<uint64_t> accessible;
     std::mt19937 rng{7};
     int fail_create_after = -1, fail_map_after = -1, fail_reserve_after = -1, fail_access_after = -1, fail_probe_after = -1;
-    int syncs = 0, stream_syncs = 0;
-    int bias_percent = 50; // chance that a new page is on side 1
+    int syncs = 0, stream_syncs = 0, creates = 0, maps = 0, unmaps = 0;
+    int bias_percent = 50;
 
+    FakeDriver() { if (model == 2) next_phys = 3; }
     static bool tick(int& counter) {
         if (counter < 0) return false;
         if (counter == 0) { counter = -1; return true; }
         --counter;
         return false;
     }
-    int create_page(uint64_t* handle, bool) override {
-        if (tick(fail_create_after) || page_side.size() >= capacity_pages) return 2;
+    size_t live_pages() const {
+        size_t n = 0;
+        for (auto& h : handles) n += (size_t)h.second.pages;
+        return n;
+    }
+    int side_of_phys(size_t k) {
+        if (model == 1) {
+            auto it = random_side.find(k);
+            if (it == random_side.end()) it = random_side.emplace(k, (int)(rng() % 100) < bias_percent).first;
+            return it->second;
+        }
+        // start side of group g: repeats the last side of group g-1 (a "flip" of the alternation) except at every 8th boundary
+        const size_t g = k / 8;
+        int start = 0;
+        for (size_t b = 1; b <= g; ++b) start ^= (b % 8 == 5) ? 0 : 1;
+        return start ^ (int)(k & 1);
+    }
+    int create_chunk(uint64_t* handle, int pages, bool) override {
+        ++creates;
+        if (tick(fail_create_after) || live_pages() + (size_t)pages > capacity_pages) return 2;
+        size_t phys = 0;
+        bool reused = false;
+        for (size_t i = holes.size(); i-- > 0 && !reused;)
+            if (holes[i].second >= (size_t)pages) {
+                phys = holes[i].first;
+                holes[i].first += (size_t)pages;
+                holes[i].second -= (size_t)pages;
+                if (holes[i].second == 0) holes.erase(holes.begin() + (long)i);
+                reused = true;
+            }
+        if (!reused) { phys = next_phys; next_phys += (size_t)pages; }
         *handle = next_handle++;
-        page_side[*handle] = (int)(rng() % 100) < bias_percent;
+        handles[*handle] = Handle{phys, pages};
         return 0;
     }
-    void release_page(uint64_t handle) override {
-        CHECK(page_side.count(handle) == 1);
-        for (auto& m : mappings) CHECK(m.second != handle);
-        page_side.erase(handle);
+    void release_chunk(uint64_t handle) override {
+        CHECK(handles.count(handle) == 1);
+        for (auto& m : mappings) CHECK(m.second.first != handle);
+        holes.emplace_back(handles[handle].phys, (size_t)handles[handle].pages);
+        handles.erase(handle);
     }
     int reserve_va(uint64_t* va, size_t bytes) override {
         if (tick(fail_reserve_after)) return 2;
@@ -174,24 +218,35 @@ struct FakeDriver : SaBackend {
             reservations.erase(it);
         }
     }
-    bool reserved(uint64_t va) {
+    bool reserved(uint64_t va, size_t bytes) {
         for (auto& r : reservations)
-            if (va >= r.first && va + kSaPageBytes <= r.first + r.second) return true;
+            if (va >= r.first && va + bytes <= r.first + r.second) return true;
         return false;
     }
-    int map_page(uint64_t va, uint64_t handle) override {
+    int map_chunk(uint64_t va, uint64_t handle, int pages) override {
+        ++maps;
         if (tick(fail_map_after)) return 1;
-        CHECK(reserved(va));
-        CHECK(mappings.count(va) == 0);
-        CHECK(page_side.count(handle) == 1);
-        for (auto& m : mappings) CHECK(m.second != handle);
-        mappings[va] = handle;
+        CHECK(reserved(va, (size_t)pages * kSaPageBytes));
+        CHECK(handles.count(handle) == 1 && handles[handle].pages == pages); // a handle is mapped whole or not at all
+        for (auto& m : mappings) CHECK(m.second.first != handle);
+        for (int k = 0; k < pages; ++k) {
+            CHECK(mappings.count(va + (uint64_t)k * kSaPageBytes) == 0);
+            mappings[va + (uint64_t)k * kSaPageBytes] = {handle, k};
+        }
         return 0;
     }
-    void unmap_page(uint64_t va) override {
+    void unmap_chunk(uint64_t va, int pages) override {
+        ++unmaps;
         CHECK(mappings.count(va) == 1);
-        mappings.erase(va);
-        accessible.erase(va);
+        if (mappings.count(va) != 1) return;
+        const uint64_t handle = mappings[va].first;
+        CHECK(mappings[va].second == 0 && handles[handle].pages == pages); // exactly one whole mapping
+        for (int k = 0; k < pages; ++k) {
+            const uint64_t a = va + (uint64_t)k * kSaPageBytes;
+            CHECK(mappings.count(a) == 1 && mappings[a].first == handle);
+            mappings.erase(a);
+            accessible.erase(a);
+        }
     }
     int set_access(uint64_t va, size_t bytes) override {
         if (tick(fail_access_after)) return 1;
@@ -201,11 +256,15 @@ struct FakeDriver : SaBackend {
         }
         return 0;
     }
+    int true_side(uint64_t va) {
+        auto& m = mappings[va];
+        return side_of_phys(handles[m.first].phys + (size_t)m.second);
+    }
     int probe_pages(const uint64_t* vas, int n, uint8_t* sides, void*) override {
         if (tick(fail_probe_after)) return 1;
         for (int i = 0; i < n; ++i) {
             CHECK(accessible.count(vas[i]) == 1);
-            sides[i] = (uint8_t)page_side[mappings[vas[i]]];
+            sides[i] = (uint8_t)true_side(vas[i]);
         }
         return 0;
     }
@@ -218,11 +277,13 @@ struct FakeDriver : SaBackend {
         for (uint64_t a = base; a < base + bytes; a += kSaPageBytes) {
             CHECK(mappings.count(a) == 1);
             CHECK(accessible.count(a) == 1);
-            wrong += page_side[mappings[a]] != (int)((a >> 21) & 1);
+            if (mappings.count(a) != 1) { ++wrong; continue; }
+            wrong += true_side(a) != (int)((a >> 21) & 1);
         }
         return wrong;
     }
 };
+int FakeDriver::default_model = 0;
 
 static void test_alloc() {
     SaAllocConfig cfg;
@@ -252,7 +313,7 @@ static void test_alloc() {
         a.free(p4, (void*)2);
         a.free(p2, (void*)1);
         size_t released = a.release_unused();
-        CHECK(released == d.next_handle * 0 + released && d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+        CHECK(released == d.next_handle * 0 + released && d.mappings.empty() && d.handles.empty() && d.reservations.empty());
         CHECK(released >= 2 * (100ull << 20));
     }
     {   // one-page and odd-page blocks
@@ -279,12 +340,12 @@ static void test_alloc() {
                 // conservation: every live handle is either mapped in a live/cached block or pooled
                 SaAllocStats st = a.stats();
                 size_t accounted = st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes;
-                CHECK(accounted == d.page_side.size());
+                CHECK(accounted == d.live_pages());
                 CHECK(d.mappings.size() == (st.bytes_live + st.bytes_cached) / kSaPageBytes);
                 if (p) a.free(p, nullptr);
                 a.free(warm, nullptr);
                 a.release_unused();
-                CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+                CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
             }
     }
     {   // out of memory: the ladder unmaps the cache, then gives up cleanly
@@ -300,7 +361,7 @@ static void test_alloc() {
         uint64_t r = a.malloc(40 * kSaPageBytes, nullptr, cfg); // cannot fit
         CHECK(r == 0);
         CHECK(a.owns(q));
-        CHECK(d.page_side.size() <= 64);
+        CHECK(d.live_pages() <= 64);
         a.free(q, nullptr);
         uint64_t s = a.malloc(60 * kSaPageBytes, nullptr, cfg); // unbalanced pool: cross-side pages allowed, still correct
         CHECK(s != 0);
@@ -322,12 +383,12 @@ static void test_alloc() {
         uint64_t big = a.malloc(64u << 20, nullptr, c2);  // no run is large enough -> trim, then map a new segment
         CHECK(big != 0);
         SaAllocStats st = a.stats();
-        CHECK(st.bytes_cached <= (16u << 20) && st.trims == 1 && d.syncs >= syncs_before + 2);
+        CHECK(st.bytes_cached <= (16u << 20) + 6 * kSaPageBytes && st.trims == 1 && d.syncs >= syncs_before + 2); // pages of a chunk shared with `small` stay
         CHECK(d.wrong_side_pages(big, 64u << 20) == 0 && d.wrong_side_pages(small, 4u << 20) == 0);
         a.free(small, nullptr);
         a.free(big, nullptr);
         a.release_unused();
-        CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
     {   // runs: split on allocation, merge on free, one skipped page when the run starts on the wrong side
         FakeDriver d;
@@ -378,24 +439,27 @@ static void test_alloc() {
     {   // trimming a run in the middle of a segment leaves the rest usable; the range is released with the last page
         FakeDriver d;
         SaAllocator a(&d, false);
-        uint64_t seg = a.malloc(30 * kSaPageBytes, nullptr, cfg);
+        uint64_t seg = a.malloc(50 * kSaPageBytes, nullptr, cfg);
         a.free(seg, nullptr);
         uint64_t x = a.malloc(10 * kSaPageBytes, nullptr, cfg);
-        uint64_t y = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        uint64_t y = a.malloc(30 * kSaPageBytes, nullptr, cfg);
         uint64_t z = a.malloc(10 * kSaPageBytes, nullptr, cfg);
-        CHECK(x && y && z);
+        CHECK(x && y && z && d.reservations.size() == 1);
         a.free(y, nullptr);
-        a.trim(0, 0); // unmaps y's pages only
-        CHECK(a.stats().bytes_cached == 0 && d.mappings.size() == 20 && d.reservations.size() == 1);
+        a.trim(0, 0); // unmaps the chunks that lie wholly inside y; pages of chunks shared with x or z stay mapped (and cached)
+        SaAllocStats st = a.stats();
+        CHECK(st.bytes_cached <= 12 * kSaPageBytes && d.reservations.size() == 1); // at most 6 pages of a 7-page chunk at either end
+        CHECK(d.mappings.size() == 20 + st.bytes_cached / kSaPageBytes);
+        CHECK(st.pages_pool[0] + st.pages_pool[1] + d.mappings.size() == d.live_pages());
         CHECK(d.wrong_side_pages(x, 10 * kSaPageBytes) == 0 && d.wrong_side_pages(z, 10 * kSaPageBytes) == 0);
-        uint64_t w = a.malloc(10 * kSaPageBytes, nullptr, cfg); // the hole is not reused: a new segment is mapped
-        CHECK(w != 0 && w != y && d.wrong_side_pages(w, 10 * kSaPageBytes) == 0);
+        uint64_t w = a.malloc(30 * kSaPageBytes, nullptr, cfg); // the hole is not reused: a new segment is mapped
+        CHECK(w != 0 && w != y && d.wrong_side_pages(w, 30 * kSaPageBytes) == 0 && d.reservations.size() == 2);
         a.free(x, nullptr);
         a.free(z, nullptr);
         a.free(w, nullptr);
         size_t released = a.release_unused();
-        CHECK(released >= 30 * kSaPageBytes);
-        CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+        CHECK(released >= 50 * kSaPageBytes);
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
     {   // skewed physical side distribution still yields correctly placed blocks
         FakeDriver d;
@@ -445,7 +509,7 @@ static void test_alloc() {
                 size_t live_bytes = 0;
                 for (auto& l : live) live_bytes += l.second;
                 CHECK(st.bytes_live == live_bytes);
-                CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.page_side.size());
+                CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.live_pages());
                 CHECK(d.mappings.size() == (st.bytes_live + st.bytes_cached) / kSaPageBytes);
             }
         }
@@ -456,9 +520,55 @@ static void test_alloc() {
                     (unsigned long long)st.trims, (unsigned long long)st.segments, (unsigned long long)st.free_runs);
         for (auto& l : live) a.free(l.first, nullptr);
         a.release_unused();
-        CHECK(d.mappings.empty() && d.page_side.empty() && d.reservations.empty());
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
     std::printf("alloc: done\n");
+}
+
+// How many driver calls growth needs under each model of the physical layout.
+static void test_alloc_chunks() {
+    SaAllocConfig cfg;
+    const size_t pages = 512; // 1 GiB
+    for (int model = 0; model < 3; ++model) {
+        FakeDriver d;
+        d.model = model;
+        if (model == 2) d.next_phys = 3;
+        SaAllocator a(&d, false);
+        uint64_t p = a.malloc(pages * kSaPageBytes, nullptr, cfg);
+        CHECK(p != 0 && d.wrong_side_pages(p, pages * kSaPageBytes) == 0);
+        SaAllocStats st = a.stats();
+        std::printf("alloc chunks: model %d: %zu pages with %d creates, %d maps, %d unmaps, %llu discarded, %llu pooled pages\n", model, pages,
+                    d.creates, d.maps, d.unmaps, (unsigned long long)st.handles_discarded,
+                    (unsigned long long)(st.pages_pool[0] + st.pages_pool[1]));
+        CHECK(st.pages_pool[0] + st.pages_pool[1] + pages == d.live_pages());
+        if (model != 1) {
+            CHECK(d.creates <= (int)pages / 3);          // two handles per group of 8 pages, plus what prediction misses cost
+            CHECK(d.maps <= (int)pages / 2);
+            CHECK(st.pages_pool[0] + st.pages_pool[1] <= 16);
+        } else {
+            CHECK(d.creates <= (int)pages * 3);           // single pages in the end, as before
+        }
+        // a second block of the same size reuses nothing and must be as cheap
+        const int creates_before = d.creates;
+        uint64_t q = a.malloc(pages * kSaPageBytes, nullptr, cfg);
+        CHECK(q != 0 && d.wrong_side_pages(q, pages * kSaPageBytes) == 0);
+        if (model != 1) CHECK(d.creates - creates_before <= (int)pages / 3);
+        // small and odd sizes
+        for (size_t n : {1, 2, 3, 5, 7, 8, 9, 15, 16, 17, 33}) {
+            uint64_t r = a.malloc(n * kSaPageBytes, nullptr, cfg);
+            CHECK(r != 0 && d.wrong_side_pages(r, n * kSaPageBytes) == 0);
+        }
+        a.free(p, nullptr);
+        a.free(q, nullptr);
+        // the freed gigabytes come back as chunks from the pool: no create at all
+        a.trim(0, 0);
+        const int creates_mid = d.creates;
+        uint64_t r = a.malloc(pages * kSaPageBytes, nullptr, cfg);
+        CHECK(r != 0 && d.wrong_side_pages(r, pages * kSaPageBytes) == 0);
+        if (model != 1) CHECK(d.creates - creates_mid <= 8);
+        std::printf("alloc chunks: model %d: re-mapping 512 pooled pages took %d creates\n", model, d.creates - creates_mid);
+    }
+    std::printf("alloc chunks: done\n");
 }
 
 // ---------------------------------------------------------------------------
@@ -530,7 +640,15 @@ static void test_topology() {
 int main(int argc, char** argv) {
     std::string what = argc > 1 ? argv[1] : "all";
     if (what == "sched" || what == "all") test_sched();
-    if (what == "alloc" || what == "all") test_alloc();
+    if (what == "alloc" || what == "all") {
+        for (int m = 0; m < 3; ++m) {
+            FakeDriver::default_model = m;
+            std::printf("alloc: simulated driver, physical side model %d\n", m);
+            test_alloc();
+        }
+        FakeDriver::default_model = 0;
+    }
+    if (what == "chunks" || what == "all") test_alloc_chunks();
     if (what == "topology" || what == "all") test_topology();
     if (g_failures) {
         std::printf("%d CHECK(s) failed\n", g_failures);

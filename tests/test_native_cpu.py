@@ -22,7 +22,7 @@ def core_binary():
     return BIN
 
 
-@pytest.mark.parametrize("suite", ["sched", "alloc", "topology"])
+@pytest.mark.parametrize("suite", ["sched", "alloc", "chunks", "topology"])
 def test_core_suite(core_binary, suite):
     r = subprocess.run([core_binary, suite], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-2000:]
