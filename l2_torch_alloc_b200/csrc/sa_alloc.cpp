@@ -261,22 +261,40 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     };
 
     std::vector<std::pair<size_t, int>> placed;
-    // 1) pooled chunks, exactly where they fit
-    {
+    // Pooled chunks, exactly where they fit: every empty stretch is filled from its left end, largest
+    // chunk first, until nothing pooled starts on the side the next slot wants.  (Going on behind a
+    // slot that cannot be served would cut the stretch into single-slot holes, which only single
+    // pages can fill; one slot is skipped only if a chunk of two pages or more fits right after it.)
+    // `leftovers_only`: stretches of a group or more are left alone, they are cheaper to fill with fresh groups.
+    auto fill_from_pool = [&](bool leftovers_only) -> bool {
         size_t i = 0;
-        while (ok && i < pages) {
-            const int room = (int)std::min<size_t>(pages - i, kSaMaxChunkPages);
-            const int w = want(i);
-            Chunk c;
-            bool found = false;
-            for (int l = room; l >= 1 && !found; --l) found = pool_pop(compressed, w, l, &c);
-            if (!found) { ++i; continue; }
-            if (!put(i, c)) { ok = false; break; }
-            placed.emplace_back(i, c.len);
-            i += c.len;
+        while (i < pages) {
+            if (slots[i].handle) { ++i; continue; }
+            size_t e = i;
+            while (e < pages && !slots[e].handle) ++e; // empty stretch [i, e)
+            if (!(leftovers_only && e - i >= (size_t)kSaGroupPages)) {
+                while (i < e) {
+                    const int room = (int)std::min<size_t>(e - i, kSaMaxChunkPages);
+                    const int w = want(i);
+                    Chunk c;
+                    bool found = false;
+                    for (int l = room; l >= 1 && !found; --l) found = pool_pop(compressed, w, l, &c);
+                    if (!found && room >= 3) { // a longer chunk one slot further on?
+                        for (int l = room - 1; l >= 2 && !found; --l) found = pool_pop(compressed, w ^ 1, l, &c);
+                        if (found) ++i;
+                    }
+                    if (!found) break;
+                    if (!put(i, c)) return false;
+                    placed.emplace_back(i, c.len);
+                    i += c.len;
+                }
+            }
+            i = e;
         }
-        if (ok) ok = open(placed);
-    }
+        return open(placed);
+    };
+    // 1) what the pool can give
+    ok = fill_from_pool(false);
 
     // 2) fresh chunks, measured where they are mapped
     struct Fresh { size_t at; int len; bool remade; };
@@ -294,6 +312,8 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
         return true;
     };
     for (int round = 0; ok && empty > 0 && memory_left && round < max_rounds; ++round) {
+        if (round > 0 && !fill_from_pool(true)) { ok = false; break; } // holes that chunks pooled meanwhile can fill
+        if (empty == 0) break;
         fresh.clear();
         // what the pages about to be created are expected to look like
         int pred_pos = phys_pos_, pred_last = phys_last_side_;
@@ -534,16 +554,25 @@ void SaAllocator::trim_locked(size_t start, size_t end) {
 // public operations
 // ---------------------------------------------------------------------------
 
-// Blocks of one page-rounded size always start on the same side.  A size seen for the first
-// time takes the side that needs no skipped page in the best-fitting free run, else the side
-// with more pooled pages (the reference's rule, sideaware.cu:1084-1088).
+// Blocks of one page-rounded size that exist at the same time always start on the same side
+// (kernels rely on equal-sized buffers having equal side patterns).  A size that has no live block
+// takes the side that needs no skipped page in the best-fitting free run, else the side with more
+// pooled pages (the reference's rule for a size it sees for the first time, sideaware.cu:1084-1088;
+// choosing again whenever the size has died out lets odd-sized blocks use up whichever side the
+// pools have too much of).
 int SaAllocator::choose_phase(size_t bytes, size_t pages, bool compressed) {
     auto it = phase_.find(bytes);
-    if (it != phase_.end()) return it->second;
+    if (it != phase_.end()) {
+        auto lc = live_of_size_.find(bytes);
+        if (lc != live_of_size_.end() && lc->second > 0) return it->second;
+        phase_.erase(it);
+    }
     int phase;
     auto fit = free_by_len_[compressed].lower_bound(pages);
+    const size_t pooled0 = pooled_pages(compressed, 0), pooled1 = pooled_pages(compressed, 1);
     if (fit != free_by_len_[compressed].end()) phase = side_bit(fit->second);
-    else phase = pooled_pages(compressed, 0) >= pooled_pages(compressed, 1) ? 0 : 1;
+    else if (pooled0 != pooled1) phase = pooled0 > pooled1 ? 0 : 1;
+    else phase = 0;
     phase_.emplace(bytes, phase);
     return phase;
 }
@@ -560,6 +589,7 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
     uint64_t p = take_from_free(pages, phase, compressed, stream);
     if (p) {
         live_[p].requested = size;
+        live_of_size_[bytes]++;
         st_.reuse_hits++;
         st_.large_allocs++;
         return p;
@@ -577,6 +607,7 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
         p = grow(pages, phase, compressed, stream, cfg);
         if (p) {
             live_[p].requested = size;
+            live_of_size_[bytes]++;
             st_.large_allocs++;
             return p;
         }
@@ -593,6 +624,8 @@ bool SaAllocator::free(uint64_t ptr, void* stream) {
     Block b = it->second;
     live_.erase(it);
     live_bytes_ -= b.pages * kSaPageBytes;
+    auto lc = live_of_size_.find(b.pages * kSaPageBytes);
+    if (lc != live_of_size_.end() && lc->second > 0) lc->second--;
     (void)stream; // the run remembers the stream the block was handed out on (sideaware.cu:1209-1214)
     Run run;
     run.pages = b.pages;

@@ -106,7 +106,7 @@ public:
     // Unmaps every free run and releases every pooled page; returns bytes released.
     size_t release_unused();
     SaAllocStats stats();
-    // side the first page of blocks of this (page-rounded) size starts on, -1 if never allocated
+    // side the first page of blocks of this (page-rounded) size starts on (fixed while such a block is live), -1 if never allocated
     int phase_of_size(size_t aligned_size);
 
 private:
@@ -165,6 +165,7 @@ private:
     std::multimap<size_t, uint64_t> free_by_len_[2];   // [compressed]: pages -> address
     std::unordered_map<uint64_t, Block> live_;
     std::unordered_map<size_t, int> phase_;
+    std::unordered_map<size_t, size_t> live_of_size_; // live blocks per page-rounded size
     size_t cached_bytes_ = 0, live_bytes_ = 0;
     uint64_t seq_ = 0;
     bool warned_cross_ = false;

@@ -496,7 +496,9 @@ static void test_alloc() {
                 for (auto& l : live) CHECK(!(p < l.first + l.second && l.first < p + bytes));
                 if (i % 7 == 0) CHECK(d.wrong_side_pages(p, bytes) == 0);
                 int ph = (int)((p >> 21) & 1);
-                if (phase_seen.count(bytes)) CHECK(phase_seen[bytes] == ph);
+                size_t same = 0;
+                for (auto& l : live) same += l.second == bytes;
+                if (same && phase_seen.count(bytes)) CHECK(phase_seen[bytes] == ph); // same side as the live blocks of that size
                 phase_seen[bytes] = ph;
                 live.push_back({p, bytes});
             } else {
@@ -567,6 +569,27 @@ static void test_alloc_chunks() {
         CHECK(r != 0 && d.wrong_side_pages(r, pages * kSaPageBytes) == 0);
         if (model != 1) CHECK(d.creates - creates_mid <= 8);
         std::printf("alloc chunks: model %d: re-mapping 512 pooled pages took %d creates\n", model, d.creates - creates_mid);
+    }
+    // many small blocks (4..12 pages each): handles per page must stay well below one
+    for (int model = 0; model < 3; model += 2) {
+        FakeDriver d;
+        d.model = model;
+        if (model == 2) d.next_phys = 3;
+        SaAllocator a(&d, false);
+        std::mt19937 rng(11);
+        size_t total = 0;
+        for (int i = 0; i < 300; ++i) {
+            size_t n = 4 + rng() % 9;
+            uint64_t r = a.malloc(n * kSaPageBytes, nullptr, cfg);
+            CHECK(r != 0 && d.wrong_side_pages(r, n * kSaPageBytes) == 0);
+            total += n;
+        }
+        SaAllocStats st = a.stats();
+        std::printf("alloc chunks: model %d: 300 small blocks, %zu pages: %d creates, %d maps, %d unmaps, %llu discarded, %llu pooled pages\n",
+                    model, total, d.creates, d.maps, d.unmaps, (unsigned long long)st.handles_discarded,
+                    (unsigned long long)(st.pages_pool[0] + st.pages_pool[1]));
+        CHECK(d.creates <= (int)total / 2);
+        CHECK(st.pages_pool[0] + st.pages_pool[1] <= total / 16); // odd-sized blocks of one start side leave a surplus of the other side
     }
     std::printf("alloc chunks: done\n");
 }
