@@ -211,6 +211,15 @@ class SideAware:
         self.rope_backward_ptr(dqkv.data_ptr(), freqs_cis.data_ptr(), B, T, n_q_heads, n_kv_heads, HS,
                                dqkv.dtype == torch.bfloat16, dqkv.device.index, torch.cuda.current_stream(dqkv.device))
 
+    def rope_precompute_freqs_into(self, freqs_cis, theta: float = 10000.0, use_scaled: bool = False) -> None:
+        """Fills an existing fp32 CUDA tensor [end, dim/2, 2] with (cos, sin)."""
+        import torch
+        assert freqs_cis.is_cuda and freqs_cis.is_contiguous() and freqs_cis.dtype == torch.float32
+        assert freqs_cis.dim() == 3 and freqs_cis.shape[2] == 2, "freqs_cis must be [end, dim/2, 2]"
+        end, half, _ = freqs_cis.shape
+        self.rope_precompute_freqs_ptr(freqs_cis.data_ptr(), 2 * half, end, float(theta), use_scaled,
+                                       freqs_cis.device.index, torch.cuda.current_stream(freqs_cis.device))
+
     def rope_precompute_freqs(self, dim: int, end: int, theta: float = 10000.0, use_scaled: bool = False, device=None):
         """The fp32 table [end, dim/2, 2] of (cos, sin) that rope_forward / rope_backward read, made on the GPU."""
         import torch

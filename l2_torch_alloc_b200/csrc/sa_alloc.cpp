@@ -267,7 +267,7 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     // pages can fill; one slot is skipped only if a chunk of two pages or more fits right after it.)
     // `leftovers_only`: stretches of a group or more are left alone, they are cheaper to fill with fresh groups.
     auto fill_from_pool = [&](bool leftovers_only) -> bool {
-        size_t i = 0;
+        size_t i = leftovers_only ? first_empty : 0; // nothing is empty before first_empty
         while (i < pages) {
             if (slots[i].handle) { ++i; continue; }
             size_t e = i;

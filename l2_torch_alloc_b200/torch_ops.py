@@ -1,5 +1,5 @@
-"""torch.ops.sideaware.* registration (the custom ops of test.py:147-157, plus rope_forward
-and silu_mul).  Kept in a module of its own WITHOUT postponed annotation evaluation:
+"""torch.ops.sideaware.* registration (the custom ops of test.py:147-157, plus rope_forward,
+rope_backward, rope_freqs and silu_mul).  Kept in a module of its own WITHOUT postponed annotation evaluation:
 torch.library.infer_schema reads the real annotation objects."""
 from typing import Optional
 
@@ -33,6 +33,9 @@ def register(sa) -> None:
     def rope_backward(dqkv: Tensor, freqs_cis: Tensor, n_q_heads: int, n_kv_heads: int) -> None:
         sa.rope_backward(dqkv, freqs_cis, n_q_heads, n_kv_heads)
 
+    def rope_freqs(freqs_cis: Tensor, theta: float, use_scaled: bool) -> None:
+        sa.rope_precompute_freqs_into(freqs_cis, theta, use_scaled)
+
     def silu_mul(out: Tensor, a: Tensor, b: Tensor, scale: float) -> None:
         sa.silu_mul(out, a, b, scale)
 
@@ -48,5 +51,6 @@ def register(sa) -> None:
     reg("elementwise", elementwise, ["out0", "out1", "out2", "out3", "sideband_tensor"])
     reg("rope_forward", rope_forward, ["qkv"])
     reg("rope_backward", rope_backward, ["dqkv"])
+    reg("rope_freqs", rope_freqs, ["freqs_cis"])
     reg("silu_mul", silu_mul, ["out"])
     _registered["lib"] = lib

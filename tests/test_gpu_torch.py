@@ -46,3 +46,30 @@ print("COMPILED-OK")
 """
     r = run_script(["-c", code])
     assert "COMPILED-OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_rope_ops_under_torch_compile():
+    """Table made on the GPU and rotation, both as custom ops inside one compiled graph, against the oracle
+    (tolerance: 1e-6 of the pair's magnitude, the fp32 tolerance of the task; the table differs from libm's by <= 1 ulp)."""
+    code = """
+import numpy as np, torch, l2_torch_alloc_b200 as pkg
+from oracle import oracle
+sa = pkg.sideaware_init()
+B, T, Nq, Nkv, HS = 2, 128, 4, 2, 64
+@torch.compile(fullgraph=True)
+def f(qkv, table):
+    torch.ops.sideaware.rope_freqs(table, 10000.0, False)
+    torch.ops.sideaware.rope_forward(qkv, table, Nq, Nkv)
+    return qkv
+x = np.random.default_rng(5).uniform(-1, 1, size=(B, T, Nq + 2 * Nkv, HS)).astype(np.float32)
+qkv = torch.from_numpy(x).cuda()
+table = torch.empty((T, HS // 2, 2), device="cuda")
+out = f(qkv, table).cpu().numpy()
+want = oracle.rope_forward_f32(x, oracle.freqs_cis(HS, T, 10000.0, 0), B, T, Nq, Nkv, HS)
+pairs = x.reshape(B, T, -1, HS // 2, 2).astype(np.float64)
+mag = np.sqrt((pairs ** 2).sum(-1, keepdims=True)).repeat(2, -1).reshape(x.shape)
+assert (np.abs(out.astype(np.float64) - want) <= 1e-6 * mag + 1e-12).all()
+print("COMPILED-ROPE-OK")
+"""
+    r = run_script(["-c", code])
+    assert "COMPILED-ROPE-OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
