@@ -3,6 +3,7 @@
     python -m l2_torch_alloc_b200.profile_case memcpy   [--mib 256] [--reps 4] [--placement aware]
     python -m l2_torch_alloc_b200.profile_case rope     [--batch 2]  [--reps 4]
     python -m l2_torch_alloc_b200.profile_case functor  [--mib 256] [--reps 4]
+    python -m l2_torch_alloc_b200.profile_case functor-jit [--mib 256] [--reps 4]   (the same functor through NVRTC)
 
 Each case touches more than the 126 MB L2 but well under 2 GB of device memory and
 launches the kernel of interest a handful of times, so a multi-pass capture ends by itself.
@@ -18,7 +19,7 @@ import l2_torch_alloc_b200 as pkg
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["memcpy", "rope", "functor"])
+    ap.add_argument("case", choices=["memcpy", "rope", "functor", "functor-jit"])
     ap.add_argument("--mib", type=int, default=256)
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--reps", type=int, default=4)
@@ -61,8 +62,17 @@ def main():
         x = torch.randn(n, device="cuda").to(torch.bfloat16)
         sa.memcpy_ptr(a, x.data_ptr(), 2 * n)
         sa.memcpy_ptr(b, x.data_ptr(), 2 * n)
-        for _ in range(args.reps):
-            sa.silu_mul_ptr(o, a, b, 0.5, n)
+        if args.case == "functor-jit":
+            import numpy as np
+            from l2_torch_alloc_b200 import functors
+            kid = sa.create_kernel(functors.silu_mul_bf16())
+            scale_bits = int(np.float32(0.5).view(np.int32))
+            sp = torch.cuda.current_stream().cuda_stream
+            for _ in range(args.reps):
+                sa.lib.sideaware_elementwise(kid, 2 * n, o, None, None, None, a, b, None, None, None, scale_bits, 0, 0, 0, sp)
+        else:
+            for _ in range(args.reps):
+                sa.silu_mul_ptr(o, a, b, 0.5, n)
         torch.cuda.synchronize()
     assert sa.error_count() == 0, sa.last_error()
     print("profile case done:", args.case, sa.summary_dict())
