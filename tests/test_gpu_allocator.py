@@ -80,6 +80,36 @@ def test_predicted_chunk_sides_match_measurement(sa):
     sa.free(p)
 
 
+def test_growth_on_fragmented_physical_memory(sa):
+    """Blocks are grown from handles of several pages whose sides are predicted, then measured.  Here other
+    allocations are interleaved and half of them freed first, so that newly created memory does not lie in the
+    order the prediction hopes for: placement must be as exact as ever, only more driver calls may be needed."""
+    sa.lib.sideaware_release_unused()
+    before = sa.stats()
+    blockers = [ch.cuda_malloc(2 * MiB) for _ in range(256)]
+    held = [sa.malloc(10 * MiB) for _ in range(24)]          # side-aware blocks in between
+    for b in blockers[::2]:
+        ch.cuda_free(b)                                       # holes of one page each in physical memory
+    sizes = [512 * MiB, 96 * MiB, 34 * MiB, 14 * MiB]
+    ptrs = [sa.malloc(n) for n in sizes]
+    for p, n in zip(ptrs, sizes):
+        assert p % (2 * MiB) == 0
+        mism = sa.verify_chunk_sides(p, n, 512, 3)
+        assert 0 <= mism <= 8, f"{mism} of 512 probed chunks of a {n >> 20} MiB block are not on the predicted side"
+    after = sa.stats()
+    pages = after["pages_created"] - before["pages_created"]
+    handles = after["handles_created"] - before["handles_created"]
+    print(f"fragmented growth: {pages} pages in {handles} handles, {after['handles_discarded'] - before['handles_discarded']} given back,"
+          f" cross-side pages {after['cross_side_pages'] - before['cross_side_pages']}")
+    assert after["cross_side_pages"] == before["cross_side_pages"]
+    assert handles <= pages
+    for p in ptrs + held:
+        sa.free(p)
+    for b in blockers[1::2]:
+        ch.cuda_free(b)
+    sa.lib.sideaware_release_unused()
+
+
 def test_release_unused_returns_memory(sa):
     import torch
     p = sa.malloc(512 * MiB)
