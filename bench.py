@@ -286,8 +286,41 @@ def cpu_rope_reference():
         fn()
         times.append(time.perf_counter() - t0)
     best = min(times)
-    return {"kind": kind, "ms": best * 1e3, "gbs": 2 * x.nbytes / best / 1e9, "cores": 1,
-            "config": "fp32 B=4 T=1024 NH=12 HS=64"}
+    res = {"kind": kind, "ms": best * 1e3, "gbs": 2 * x.nbytes / best / 1e9, "cores": 1,
+           "config": "fp32 B=4 T=1024 NH=12 HS=64"}
+    # the same function over all host cores: the batch is cut into shards (the rotation of one batch entry does
+    # not depend on the others) and every shard is one call from its own thread (ctypes releases the GIL)
+    cores = os.cpu_count() or 1
+    Bm = 4 * cores
+    xm = np.random.default_rng(0xB200 + 1).uniform(-1, 1, size=(Bm, T, 3 * NH, HS)).astype(np.float32)
+    om = np.empty_like(xm)
+    per = Bm // cores
+
+    def shard(i):
+        xi, oi = xm[i * per:(i + 1) * per], om[i * per:(i + 1) * per]
+        if kind == "reference":
+            oracle.ref().ref_apply_rotary_emb_forward(oracle._ptr(oi, oracle._f32p), oracle._ptr(xi, oracle._f32p),
+                                                      oracle._ptr(tab, oracle._f32p), per, T, NH, HS)
+        else:
+            oracle.lib().oracle_rope_forward_f32(oracle._ptr(oi, oracle._f32p), oracle._ptr(xi, oracle._f32p),
+                                                 oracle._ptr(tab, oracle._f32p), per, T, NH, NH, HS)
+
+    def all_cores():
+        ts = [threading.Thread(target=shard, args=(i,)) for i in range(cores)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+
+    all_cores()
+    mt = []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        all_cores()
+        mt.append(time.perf_counter() - t0)
+    res["all_cores"] = {"cores": cores, "ms": min(mt) * 1e3, "gbs": 2 * xm.nbytes / min(mt) / 1e9,
+                        "config": f"fp32 B={Bm} T=1024 NH=12 HS=64, one shard of {per} per thread"}
+    return res
 
 
 def run_reference(args, ranks):
@@ -712,9 +745,10 @@ def run_ours(args, ranks):
         if ranks.world == 1:
             threads = os.cpu_count() or 1
             v, times = cpu_memcpy_gbs(MEMCPY_BYTES, 12, threads)
+            v1, _ = cpu_memcpy_gbs(MEMCPY_BYTES, 4, 1)
             cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
                    "sample": f"12 x 1 GiB libc memcpy over {threads} threads (the reference has no CPU memcpy)",
-                   "rope": cpu_rope_reference()}
+                   "one_thread_gbs": v1, "rope": cpu_rope_reference()}
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": ranks.world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": worst_ms / args.steps, "higher_is_better": True, "scaling": "weak",
