@@ -357,48 +357,63 @@ def run_reference(args, ranks):
 # ---------------------------------------------------------------------------
 # allocator churn and power (extras, rank 0 at N = 1)
 # ---------------------------------------------------------------------------
-def allocator_churn(lib, rt, dev, sp, ops, use_runtime_pool=False):
+def allocator_churn(lib, rt, dev, sp, ops, arm="sideaware"):
     """`ops` seeded malloc/free calls, sizes log-uniform 4 KiB .. 2 GiB rounded up to 16 B, live set capped
-    at 32 GiB, through sideaware_malloc_auto / sideaware_free_auto (what torch's pluggable allocator calls),
-    or through cudaMallocAsync / cudaFreeAsync for comparison."""
+    at 32 GiB.  arm "sideaware": sideaware_malloc_auto / sideaware_free_auto (what torch's pluggable allocator
+    calls); for comparison "cudaMallocAsync": the runtime's stream-ordered pool, "torch": torch's own caching
+    allocator through torch.empty (this process has not installed the pluggable allocator)."""
     import ctypes
     import numpy as np
+    import torch
     rng = np.random.default_rng(0xB200 + 5)
     live, live_bytes, peak = [], 0, 0
     t_malloc_small, t_malloc_large, t_free = [], [], []
     p = ctypes.c_void_p()
+
+    def do_malloc(size):
+        if arm == "cudaMallocAsync":
+            rc = rt.cudaMallocAsync(ctypes.byref(p), size, sp)
+            return p.value if rc == 0 else None
+        if arm == "torch":
+            try:
+                return torch.empty(size, dtype=torch.uint8, device="cuda")
+            except torch.OutOfMemoryError:
+                return None
+        return lib.sideaware_malloc_auto(size, dev, sp)
+
+    def do_free(ptr, size):
+        if arm == "cudaMallocAsync":
+            rt.cudaFreeAsync(ptr, sp)
+        elif arm == "torch":
+            del ptr  # the caller's reference is dropped as well (see below)
+        else:
+            lib.sideaware_free_auto(ptr, size, dev, sp)
+
     t_start = time.perf_counter()
     for _ in range(ops):
         if live and (live_bytes > (32 << 30) or rng.random() < 0.45):
             ptr, size = live.pop(int(rng.integers(len(live))))
             t0 = time.perf_counter_ns()
-            if use_runtime_pool:
-                rt.cudaFreeAsync(ptr, sp)
-            else:
-                lib.sideaware_free_auto(ptr, size, dev, sp)
+            do_free(ptr, size)
+            ptr = None
             t_free.append(time.perf_counter_ns() - t0)
             live_bytes -= size
         else:
             size = int(np.exp(rng.uniform(np.log(4096), np.log(2 << 30))))
             size = (size + 15) // 16 * 16
             t0 = time.perf_counter_ns()
-            if use_runtime_pool:
-                rc = rt.cudaMallocAsync(ctypes.byref(p), size, sp)
-                ptr = p.value if rc == 0 else None
-            else:
-                ptr = lib.sideaware_malloc_auto(size, dev, sp)
+            ptr = do_malloc(size)
             dt = time.perf_counter_ns() - t0
-            if not ptr:
+            if ptr is None or (not isinstance(ptr, torch.Tensor) and not ptr):
                 continue
             (t_malloc_large if size >= (8 << 20) else t_malloc_small).append(dt)
             live.append((ptr, size))
             live_bytes += size
             peak = max(peak, live_bytes)
-    for ptr, size in live:
-        if use_runtime_pool:
-            rt.cudaFreeAsync(ptr, sp)
-        else:
-            lib.sideaware_free_auto(ptr, size, dev, sp)
+    while live:
+        ptr, size = live.pop()
+        do_free(ptr, size)
+        ptr = None
     elapsed = time.perf_counter() - t_start
 
     def pct(v, q):
@@ -736,8 +751,12 @@ def run_ours(args, ranks):
         churn["sideaware"]["stats"] = sa.stats()
         lib.sideaware_release_unused()
         torch.cuda.synchronize()
-        churn["cudaMallocAsync"] = allocator_churn(lib, rt, dev, sp, args.churn_ops, use_runtime_pool=True)
+        churn["cudaMallocAsync"] = allocator_churn(lib, rt, dev, sp, args.churn_ops, arm="cudaMallocAsync")
         torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        churn["torch_caching_allocator"] = allocator_churn(lib, rt, dev, sp, args.churn_ops, arm="torch")
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
 
     line = None
     if ranks.rank == 0:
