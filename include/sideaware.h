@@ -180,6 +180,7 @@ typedef struct sideaware_stats_t {
     unsigned long long kernel_wait_timeouts;   /* bounded waits inside kernels that ran out (0 in a healthy run) */
     unsigned long long handles_created;        /* cuMemCreate calls; pages_created counts the 2 MiB pages they hold */
     unsigned long long handles_discarded;      /* handles given back because their pages' sides did not alternate */
+    unsigned long long extensions;             /* blocks made of a segment's last free run plus newly mapped pages */
 } sideaware_stats_t;
 void sideaware_get_stats(sideaware_stats_t* out);
 

@@ -160,8 +160,8 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
 // growing and shrinking the mapped set
 // ---------------------------------------------------------------------------
 
-// Maps a new segment of exactly `pages` pages whose first page is on side `phase` and hands all
-// of it out as one block.
+// Fills the empty slots [lo, hi) of a segment with physical memory.  True if all of them are
+// mapped and accessible afterwards; otherwise everything this call mapped is taken out again.
 //
 // 1) Pooled chunks (their sides are known) are put where they fit, largest first.
 // 2) The rest is created fresh, a few chunks per round, each mapped where the pages seen so far
@@ -172,24 +172,16 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
 //    first (sideaware.cu:947-1019), at one more cuMemSetAccess and cuMemUnmap per page.
 // 3) If device memory ran out on the way, pooled chunks of the other side fill what is left
 //    (slower, still correct).
-uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg) {
-    (void)cfg;
-    std::unique_ptr<Segment> seg(new Segment());
-    seg->compressed = compressed;
-    seg->num_pages = pages;
-    // one spare page of address space lets us pick the phase of bit 21
-    seg->reserved_bytes = (pages + 1) * kSaPageBytes;
-    if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
-    seg->base = seg->reserved;
-    if (side_bit(seg->base) != phase) seg->base += kSaPageBytes;
-    seg->pages.assign(pages, Slot{});
+bool SaAllocator::map_slots(Segment* seg, size_t lo, size_t hi, void* stream) {
+    const bool compressed = seg->compressed;
     std::vector<Slot>& slots = seg->pages;
     auto slot_va = [&](size_t i) { return seg->base + i * kSaPageBytes; };
     auto want = [&](size_t i) { return side_bit(slot_va(i)); };
+    const size_t pages = hi; // scans below stop here
 
     bool ok = true;
-    size_t empty = pages;
-    size_t first_empty = 0;
+    size_t empty = hi - lo;
+    size_t first_empty = lo;
 
     // maps chunk `c` at slot `at`; a chunk that cannot be mapped goes back to the pool (or the driver)
     auto put = [&](size_t at, const Chunk& c) -> bool {
@@ -267,7 +259,7 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     // pages can fill; one slot is skipped only if a chunk of two pages or more fits right after it.)
     // `leftovers_only`: stretches of a group or more are left alone, they are cheaper to fill with fresh groups.
     auto fill_from_pool = [&](bool leftovers_only) -> bool {
-        size_t i = leftovers_only ? first_empty : 0; // nothing is empty before first_empty
+        size_t i = leftovers_only ? first_empty : lo; // nothing is empty before first_empty
         while (i < pages) {
             if (slots[i].handle) { ++i; continue; }
             size_t e = i;
@@ -303,7 +295,7 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     std::vector<uint8_t> sides;
     std::vector<Chunk> displaced;
     bool memory_left = true;
-    const int max_rounds = 64 + (int)(pages / 4);
+    const int max_rounds = 64 + (int)((hi - lo) / 4);
     auto leftmost = [&](int len, size_t* at) -> bool {
         size_t a0 = 0, a1 = 0;
         const bool h0 = find_place(len, 0, &a0), h1 = find_place(len, 1, &a1);
@@ -438,7 +430,7 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     }
     // 3) device memory ran out: whatever is pooled fills the rest, whichever side it is on
     if (ok && empty > 0) {
-        size_t i = 0;
+        size_t i = lo;
         while (ok && i < pages) {
             if (slots[i].handle) { ++i; continue; }
             int room = 0;
@@ -461,11 +453,39 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
         if (ok) ok = open(placed);
     }
     if (!ok) {
-        for (size_t i = 0; i < pages; ++i) {
+        for (size_t i = lo; i < hi; ++i) {
             if (!slots[i].handle || slots[i].idx != 0) continue;
             Chunk c = lift(i);
             pool_push(compressed, c); // a chunk that was never measured goes back to the driver
         }
+        return false;
+    }
+    return true;
+}
+
+// Extra address space reserved behind a new segment, so that it can be extended later.
+static size_t segment_slack(size_t pages) { return std::min<size_t>(std::max<size_t>(pages, 64), 4096); }
+
+// Maps a new segment of `pages` pages whose first page is on side `phase` and hands all of it out
+// as one block.
+uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg) {
+    (void)cfg;
+    std::unique_ptr<Segment> seg(new Segment());
+    seg->compressed = compressed;
+    // one spare page of address space lets us pick the phase of bit 21
+    seg->capacity = pages + segment_slack(pages);
+    seg->reserved_bytes = (seg->capacity + 1) * kSaPageBytes;
+    if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) {
+        // address space is short: no room to extend, then
+        seg->capacity = pages;
+        seg->reserved_bytes = (pages + 1) * kSaPageBytes;
+        if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
+    }
+    seg->base = seg->reserved;
+    if (side_bit(seg->base) != phase) seg->base += kSaPageBytes;
+    seg->pages.assign(pages, Slot{});
+    seg->num_pages = pages;
+    if (!map_slots(seg.get(), 0, pages, stream)) {
         be_->free_va(seg->reserved, seg->reserved_bytes);
         return 0;
     }
@@ -478,6 +498,62 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     live_.emplace(base, b);
     live_bytes_ += pages * kSaPageBytes;
     segments_.push_back(std::move(seg));
+    return base;
+}
+
+// A request that no free run can hold, but a free run at the END of a segment can if the segment
+// grows: only the missing pages are mapped (behind the run, in the address space reserved with
+// the segment), instead of a whole new segment.  Takes the run that leaves the fewest pages to map.
+uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* stream) {
+    Segment* best = nullptr;
+    uint64_t best_va = 0;
+    size_t best_have = 0;
+    for (auto& sp : segments_) {
+        Segment* seg = sp.get();
+        if (seg->compressed != compressed || seg->num_pages >= seg->capacity) continue;
+        const uint64_t end = seg->base + seg->num_pages * kSaPageBytes;
+        auto it = free_.lower_bound(end);
+        if (it == free_.begin()) continue;
+        --it;
+        if (it->second.seg != seg || it->first + it->second.pages * kSaPageBytes != end) continue;
+        const size_t skip = side_bit(it->first) == phase ? 0 : 1;
+        if (it->second.pages <= skip) continue;
+        const size_t have = it->second.pages - skip;
+        if (have >= pages) continue; // take_from_free would have served it
+        if (seg->num_pages + (pages - have) > seg->capacity) continue;
+        if (have > best_have) { best = seg; best_va = it->first; best_have = have; }
+    }
+    if (!best) return 0;
+    auto it = free_.find(best_va);
+    const Run run = it->second;
+    erase_free(it);
+    const size_t skip = run.pages - best_have;
+    const size_t extra = pages - best_have;
+    const size_t old_pages = best->num_pages;
+    best->pages.resize(old_pages + extra, Slot{});
+    if (!map_slots(best, old_pages, old_pages + extra, stream)) {
+        best->pages.resize(old_pages);
+        insert_free(best_va, run);
+        return 0;
+    }
+    best->num_pages = old_pages + extra;
+    best->mapped_pages += extra;
+    if (skip) {
+        Run head = run;
+        head.pages = 1;
+        insert_free(best_va, head);
+    }
+    // work queued by the previous user(s) of the run must be done before a different stream touches it
+    if (run.mixed) be_->device_sync();
+    else if (run.stream != stream) be_->stream_sync(run.stream);
+    const uint64_t base = best_va + skip * kSaPageBytes;
+    Block b;
+    b.pages = pages;
+    b.seg = best;
+    b.stream = stream;
+    live_.emplace(base, b);
+    live_bytes_ += pages * kSaPageBytes;
+    st_.extensions++;
     return base;
 }
 
@@ -595,7 +671,8 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
         return p;
     }
     // 2..4) the ladder of sideaware.cu:1233-1252: unmap free memory above the threshold, unmap
-    // all of it, give all pooled pages back to the driver; try to map a new segment after each
+    // all of it, give all pooled pages back to the driver; try to grow the mapped set after each.
+    // Growing: a free run at the end of a segment plus as many new pages as are missing, else a new segment.
     for (int step = 0; step < 3; ++step) {
         if (step == 0) trim_locked(cfg.trim_start, cfg.trim_end);
         else if (step == 1) trim_locked(0, 0);
@@ -604,7 +681,8 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
             release_pools();
             be_->device_sync();
         }
-        p = grow(pages, phase, compressed, stream, cfg);
+        p = step == 0 ? extend(pages, phase, compressed, stream) : 0;
+        if (!p) p = grow(pages, phase, compressed, stream, cfg);
         if (p) {
             live_[p].requested = size;
             live_of_size_[bytes]++;

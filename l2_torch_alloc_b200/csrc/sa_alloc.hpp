@@ -86,6 +86,7 @@ struct SaAllocStats {
     uint64_t segments = 0, free_runs = 0;
     uint64_t handles_created = 0;   // cuMemCreate calls (pages_created counts their pages)
     uint64_t handles_discarded = 0; // created, measured, found unusable (pages do not alternate), given back
+    uint64_t extensions = 0;        // blocks made of a segment's last free run plus newly mapped pages
 };
 
 class SaAllocator {
@@ -117,6 +118,7 @@ private:
     struct Segment {
         uint64_t reserved = 0, base = 0;
         size_t reserved_bytes = 0, num_pages = 0, mapped_pages = 0;
+        size_t capacity = 0; // slots the reserved address range has room for (num_pages of them in use)
         bool compressed = false;
         std::vector<Slot> pages;
     };
@@ -135,6 +137,8 @@ private:
 
     uint64_t take_from_free(size_t pages, int phase, bool compressed, void* stream);
     uint64_t grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg);
+    uint64_t extend(size_t pages, int phase, bool compressed, void* stream);
+    bool map_slots(Segment* seg, size_t lo, size_t hi, void* stream);
     void insert_free(uint64_t va, Run run);
     void erase_free(std::map<uint64_t, Run>::iterator it);
     void unmap_run(uint64_t va, const Run& run);

@@ -461,6 +461,52 @@ static void test_alloc() {
         CHECK(released >= 50 * kSaPageBytes);
         CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
+    {   // a request larger than the free run at the end of a segment extends the segment by the missing pages only
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t p = a.malloc(20 * kSaPageBytes, nullptr, cfg);
+        CHECK(p != 0);
+        a.free(p, nullptr);
+        const size_t live_before = d.live_pages();
+        uint64_t q = a.malloc(30 * kSaPageBytes, nullptr, cfg);
+        SaAllocStats st = a.stats();
+        CHECK(q != 0 && d.wrong_side_pages(q, 30 * kSaPageBytes) == 0);
+        CHECK(st.extensions == 1 && st.segments == 1 && d.reservations.size() == 1);
+        CHECK(q == p || q == p + kSaPageBytes);                       // the old run, or the old run less a skipped page
+        CHECK(d.live_pages() <= live_before + 11 + 8);                 // about 10 new pages, not 30
+        CHECK(st.bytes_live == 30 * kSaPageBytes);
+        CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.live_pages());
+        a.free(q, nullptr);
+        CHECK(a.stats().free_runs == 1);                               // one run again, longer now
+        uint64_t r = a.malloc(400 * kSaPageBytes, nullptr, cfg);      // beyond the reserved room: a new segment
+        CHECK(r != 0 && a.stats().segments == 2 && a.stats().extensions == 1);
+        a.free(r, nullptr);
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
+    }
+    {   // fault injection on the extension path: the old run must survive a failed extension
+        for (int kind = 0; kind < 5; ++kind)
+            for (int k = 0; k < 12; k += 1) {
+                FakeDriver d;
+                SaAllocator a(&d, false);
+                uint64_t p = a.malloc(16 * kSaPageBytes, nullptr, cfg);
+                a.free(p, nullptr);
+                int* knob = kind == 0 ? &d.fail_create_after : kind == 1 ? &d.fail_map_after : kind == 2 ? &d.fail_reserve_after
+                          : kind == 3 ? &d.fail_access_after : &d.fail_probe_after;
+                *knob = k;
+                uint64_t q = a.malloc(40 * kSaPageBytes, nullptr, cfg);
+                if (q) CHECK(d.wrong_side_pages(q, 40 * kSaPageBytes) >= 0);
+                SaAllocStats st = a.stats();
+                CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.live_pages());
+                CHECK(d.mappings.size() == (st.bytes_live + st.bytes_cached) / kSaPageBytes);
+                if (q) a.free(q, nullptr);
+                uint64_t again = a.malloc(16 * kSaPageBytes, nullptr, cfg); // still served without the driver's help or with it, but correctly
+                CHECK(again != 0 && d.wrong_side_pages(again, 16 * kSaPageBytes) == 0);
+                a.free(again, nullptr);
+                a.release_unused();
+                CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
+            }
+    }
     {   // skewed physical side distribution still yields correctly placed blocks
         FakeDriver d;
         d.bias_percent = 80;
