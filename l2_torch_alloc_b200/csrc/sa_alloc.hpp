@@ -151,6 +151,7 @@ private:
     bool pool_pop(bool compressed, int side, int len, Chunk* out);
     size_t pooled_pages(bool compressed, int side) const;
     void note_fresh_sides(const uint8_t* sides, int n);
+    int expected_plain_gap() const;
 
     SaBackend* be_;
     bool comp_ok_;
@@ -161,6 +162,9 @@ private:
     // decides how few driver calls growth needs): pages since the last group boundary, the side
     // of the newest page, and how the latest chunks fared.
     int phys_pos_ = 0, phys_last_side_ = -1;
+    static constexpr int kGapHistory = 8;
+    int groups_since_plain_ = 0;      // group boundaries since the last one that did not repeat a side
+    int plain_gaps_[kGapHistory] = {0}, plain_gap_count_ = 0; // distances between such boundaries, newest overwrite oldest
     int round_pages_ = kSaGroupPages; // pages created per probing round: grows while predictions hold
     int recent_bad_ = 0;              // discarded handles, decaying
     int singles_left_ = 0;            // > 0: that many more creations as single pages
