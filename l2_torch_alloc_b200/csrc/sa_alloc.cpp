@@ -493,8 +493,10 @@ bool SaAllocator::map_slots(Segment* seg, size_t lo, size_t hi, void* stream) {
     return true;
 }
 
-// Extra address space reserved behind a new segment, so that it can be extended later.
-static size_t segment_slack(size_t pages) { return std::min<size_t>(std::max<size_t>(pages, 64), 4096); }
+// Address space reserved behind a new segment: later blocks are put there, next to the earlier
+// ones, so that freed neighbours merge into runs that larger requests can use (separate segments
+// never merge).  Address space is plentiful (47 bits); nothing is mapped until it is needed.
+static size_t segment_slack(size_t pages) { return std::max<size_t>(3 * pages, 4096); }
 
 // Maps a new segment of `pages` pages whose first page is on side `phase` and hands all of it out
 // as one block.
@@ -531,52 +533,87 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     return base;
 }
 
-// A request that no free run can hold, but a free run at the END of a segment can if the segment
-// grows: only the missing pages are mapped (behind the run, in the address space reserved with
-// the segment), instead of a whole new segment.  Takes the run that leaves the fewest pages to map.
+// Puts a block behind the last page of an existing segment (in the address space reserved with
+// it) instead of opening a new segment.  If the segment ends in a free run, the run is part of the
+// block and only the missing pages are mapped: the segment that leaves the fewest pages to map is
+// taken.  Otherwise the block starts right behind the segment's last block (one page further if
+// that slot is on the wrong side; the skipped page is mapped too and becomes a free run, so that
+// the neighbours can still merge across it).
 uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* stream) {
     Segment* best = nullptr;
     uint64_t best_va = 0;
-    size_t best_have = 0;
+    size_t best_have = 0, best_room = 0;
     for (auto& sp : segments_) {
         Segment* seg = sp.get();
         if (seg->compressed != compressed || seg->num_pages >= seg->capacity) continue;
         const uint64_t end = seg->base + seg->num_pages * kSaPageBytes;
+        size_t have = 0;
+        uint64_t run_va = 0;
         auto it = free_.lower_bound(end);
-        if (it == free_.begin()) continue;
-        --it;
-        if (it->second.seg != seg || it->first + it->second.pages * kSaPageBytes != end) continue;
-        const size_t skip = side_bit(it->first) == phase ? 0 : 1;
-        if (it->second.pages <= skip) continue;
-        const size_t have = it->second.pages - skip;
+        if (it != free_.begin()) {
+            --it;
+            if (it->second.seg == seg && it->first + it->second.pages * kSaPageBytes == end) {
+                const size_t skip = side_bit(it->first) == phase ? 0 : 1;
+                if (it->second.pages > skip) {
+                    have = it->second.pages - skip;
+                    run_va = it->first;
+                }
+            }
+        }
         if (have >= pages) continue; // take_from_free would have served it
-        if (seg->num_pages + (pages - have) > seg->capacity) continue;
-        if (have > best_have) { best = seg; best_va = it->first; best_have = have; }
+        const size_t lead = have ? 0 : (side_bit(end) == phase ? 0 : 1);
+        if (seg->num_pages + lead + (pages - have) > seg->capacity) continue;
+        const size_t room = seg->capacity - seg->num_pages;
+        if (!best || have > best_have || (have == best_have && room > best_room)) {
+            best = seg;
+            best_va = run_va;
+            best_have = have;
+            best_room = room;
+        }
     }
     if (!best) return 0;
-    auto it = free_.find(best_va);
-    const Run run = it->second;
-    erase_free(it);
-    const size_t skip = run.pages - best_have;
-    const size_t extra = pages - best_have;
+    Run run;
+    size_t skip = 0;
+    if (best_have) {
+        auto it = free_.find(best_va);
+        run = it->second;
+        erase_free(it);
+        skip = run.pages - best_have;
+    }
     const size_t old_pages = best->num_pages;
+    const uint64_t end = best->base + old_pages * kSaPageBytes;
+    const size_t lead = best_have ? 0 : (side_bit(end) == phase ? 0 : 1);
+    const size_t extra = lead + (pages - best_have);
     best->pages.resize(old_pages + extra, Slot{});
     if (!map_slots(best, old_pages, old_pages + extra, stream)) {
         best->pages.resize(old_pages);
-        insert_free(best_va, run);
+        if (best_have) insert_free(best_va, run);
         return 0;
     }
     best->num_pages = old_pages + extra;
     best->mapped_pages += extra;
-    if (skip) {
-        Run head = run;
-        head.pages = 1;
-        insert_free(best_va, head);
+    uint64_t base;
+    if (best_have) {
+        if (skip) {
+            Run head = run;
+            head.pages = 1;
+            insert_free(best_va, head);
+        }
+        // work queued by the previous user(s) of the run must be done before a different stream touches it
+        if (run.mixed) be_->device_sync();
+        else if (run.stream != stream) be_->stream_sync(run.stream);
+        base = best_va + skip * kSaPageBytes;
+    } else {
+        if (lead) {
+            Run gap;
+            gap.pages = 1;
+            gap.seg = best;
+            gap.freed_seq = ++seq_;
+            gap.stream = stream;
+            insert_free(end, gap);
+        }
+        base = end + lead * kSaPageBytes;
     }
-    // work queued by the previous user(s) of the run must be done before a different stream touches it
-    if (run.mixed) be_->device_sync();
-    else if (run.stream != stream) be_->stream_sync(run.stream);
-    const uint64_t base = best_va + skip * kSaPageBytes;
     Block b;
     b.pages = pages;
     b.seg = best;
@@ -624,6 +661,9 @@ void SaAllocator::unmap_run(uint64_t va, const Run& run) {
         }
     }
     keep_until(last);
+    // slots that fell empty at the end of the segment are room to grow into again
+    while (seg->num_pages > 0 && !seg->pages[seg->num_pages - 1].handle) --seg->num_pages;
+    seg->pages.resize(seg->num_pages);
     if (seg->mapped_pages == 0) {
         be_->free_va(seg->reserved, seg->reserved_bytes);
         for (size_t k = 0; k < segments_.size(); ++k)
@@ -635,23 +675,48 @@ void SaAllocator::unmap_run(uint64_t va, const Run& run) {
     }
 }
 
+// pages of the run that belong to chunks lying wholly inside it (only such chunks can be unmapped)
+size_t SaAllocator::reclaimable_pages(uint64_t va, const Run& run) const {
+    const Segment* seg = run.seg;
+    const size_t first = (size_t)((va - seg->base) / kSaPageBytes), last = first + run.pages;
+    size_t n = 0, i = first;
+    while (i < last) {
+        const Slot& sl = seg->pages[i];
+        const size_t c0 = i - sl.idx, c1 = c0 + sl.len;
+        if (c0 >= first && c1 <= last) n += sl.len;
+        i = std::min(c1, last);
+    }
+    return n;
+}
+
+// If more than `start` bytes could be given back (free runs, less the pieces of chunks that reach
+// into live neighbours: those stay mapped whatever happens): unmaps free runs, least recently
+// freed first, until at most `end` bytes could still be given back.
 void SaAllocator::trim_locked(size_t start, size_t end) {
     if (cached_bytes_ <= start || cached_bytes_ == 0) return;
+    struct Cand { uint64_t seq, va; size_t pages; };
+    std::vector<Cand> order;
+    order.reserve(free_.size());
+    size_t reclaimable = 0;
+    for (auto& kv : free_) {
+        const size_t n = reclaimable_pages(kv.first, kv.second);
+        if (!n) continue;
+        order.push_back(Cand{kv.second.freed_seq, kv.first, n});
+        reclaimable += n * kSaPageBytes;
+    }
+    if (reclaimable == 0 || reclaimable <= start) return;
+    std::sort(order.begin(), order.end(), [](const Cand& a, const Cand& b) { return a.seq < b.seq; });
     be_->device_sync(); // freed pages may still be in use by queued work
     st_.trims++;
-    // least recently freed first
-    std::vector<std::pair<uint64_t, uint64_t>> order; // (freed_seq, va)
-    order.reserve(free_.size());
-    for (auto& kv : free_) order.emplace_back(kv.second.freed_seq, kv.first);
-    std::sort(order.begin(), order.end());
     for (auto& o : order) {
-        if (cached_bytes_ <= end) break;
-        auto it = free_.find(o.second);
-        if (it == free_.end()) continue;
+        if (reclaimable <= end) break;
+        auto it = free_.find(o.va);
+        if (it == free_.end()) continue; // merged into a neighbour that was handled before
         const uint64_t va = it->first;
         const Run run = it->second;
         erase_free(it);
         unmap_run(va, run);
+        reclaimable -= std::min(reclaimable, o.pages * kSaPageBytes);
     }
     be_->device_sync();
 }

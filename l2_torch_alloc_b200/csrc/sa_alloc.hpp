@@ -6,9 +6,9 @@
 // segment.  Because the bit-21 rule holds for every page of a segment, any run can be handed out
 // as long as it STARTS on the side that blocks of that size start on (equal sizes => equal side
 // patterns), which costs at most one skipped page.  Freed runs stay mapped, coalesce with their
-// neighbours and are reused best-fit.  A segment reserves address space behind its last page, so a
-// request that only the free run at its end could almost hold is served by mapping the missing
-// pages there instead of a whole new segment.
+// neighbours and are reused best-fit.  A segment reserves address space behind its last page: a
+// request that no free run can hold is put there (using the free run at the segment's end, if any,
+// and mapping only what is missing), so blocks lie next to each other and merge when freed.
 //
 // Why not remap pages into a fresh range per block, as the reference does
 // (sideaware.cu:1036-1197)?  On B200 the driver needs about 170-300 us in cuMemSetAccess and 90 us
@@ -103,8 +103,8 @@ public:
     // true if `ptr` was a live block of this allocator (its pages are now free, still mapped)
     bool free(uint64_t ptr, void* stream);
     bool owns(uint64_t ptr);
-    // If more than `start` bytes are free-but-mapped: unmap free runs, least recently freed
-    // first, until at most `end` bytes are.
+    // If more than `start` bytes are free-but-mapped and could be unmapped: unmap free runs, least
+    // recently freed first, until at most `end` such bytes are left.
     void trim(size_t start, size_t end);
     // Unmaps every free run and releases every pooled page; returns bytes released.
     size_t release_unused();
@@ -145,6 +145,7 @@ private:
     void erase_free(std::map<uint64_t, Run>::iterator it);
     void unmap_run(uint64_t va, const Run& run);
     void trim_locked(size_t start, size_t end);
+    size_t reclaimable_pages(uint64_t va, const Run& run) const;
     void release_pools();
     int choose_phase(size_t bytes, size_t pages, bool compressed);
     void pool_push(bool compressed, const Chunk& c);

@@ -373,20 +373,25 @@ static void test_alloc() {
         c2.trim_start = 64u << 20;
         c2.trim_end = 16u << 20;
         std::vector<uint64_t> ps;
-        for (int i = 0; i < 10; ++i) ps.push_back(a.malloc((size_t)(8 + 2 * i) << 20, nullptr, c2));
-        for (uint64_t p : ps) a.free(p, nullptr);
-        CHECK(a.stats().bytes_cached == 170ull << 20);
+        for (int i = 0; i < 12; ++i) ps.push_back(a.malloc((size_t)(16 + 2 * i) << 20, nullptr, c2));
+        for (int i = 0; i < 12; i += 2) a.free(ps[i], nullptr); // every other block: six separate runs of 16..36 MiB
+        const size_t cached_all = a.stats().bytes_cached;
+        CHECK(cached_all >= (156ull << 20) && cached_all <= (156ull << 20) + 12 * kSaPageBytes);
         int syncs_before = d.syncs;
         uint64_t small = a.malloc(4u << 20, nullptr, c2); // fits into a free run: no driver call, no trim
         CHECK(small != 0 && a.stats().trims == 0 && d.syncs == syncs_before);
-        CHECK(a.stats().bytes_cached == 166ull << 20);
-        uint64_t big = a.malloc(64u << 20, nullptr, c2);  // no run is large enough -> trim, then map a new segment
+        CHECK(a.stats().bytes_cached == cached_all - (4u << 20));
+        uint64_t big = a.malloc(64u << 20, nullptr, c2);  // no run is large enough -> trim, then grow
         CHECK(big != 0);
         SaAllocStats st = a.stats();
-        CHECK(st.bytes_cached <= (16u << 20) + 6 * kSaPageBytes && st.trims == 1 && d.syncs >= syncs_before + 2); // pages of a chunk shared with `small` stay
+        // whole chunks inside the free runs are unmapped; pages of chunks shared with live neighbours stay (up to 6 at either end of a run)
+        CHECK(st.trims == 1 && d.syncs >= syncs_before + 2);
+        CHECK(st.bytes_cached <= (16u << 20) + 6 * 12 * kSaPageBytes && st.bytes_cached < cached_all / 2);
+        CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.live_pages());
         CHECK(d.wrong_side_pages(big, 64u << 20) == 0 && d.wrong_side_pages(small, 4u << 20) == 0);
         a.free(small, nullptr);
         a.free(big, nullptr);
+        for (int i = 1; i < 12; i += 2) a.free(ps[i], nullptr);
         a.release_unused();
         CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
@@ -452,8 +457,8 @@ static void test_alloc() {
         CHECK(d.mappings.size() == 20 + st.bytes_cached / kSaPageBytes);
         CHECK(st.pages_pool[0] + st.pages_pool[1] + d.mappings.size() == d.live_pages());
         CHECK(d.wrong_side_pages(x, 10 * kSaPageBytes) == 0 && d.wrong_side_pages(z, 10 * kSaPageBytes) == 0);
-        uint64_t w = a.malloc(30 * kSaPageBytes, nullptr, cfg); // the hole is not reused: a new segment is mapped
-        CHECK(w != 0 && w != y && d.wrong_side_pages(w, 30 * kSaPageBytes) == 0 && d.reservations.size() == 2);
+        uint64_t w = a.malloc(30 * kSaPageBytes, nullptr, cfg); // the hole is not reused: the block goes behind z, into the room reserved with the segment
+        CHECK(w != 0 && w != y && w > z && d.wrong_side_pages(w, 30 * kSaPageBytes) == 0 && d.reservations.size() == 1);
         a.free(x, nullptr);
         a.free(z, nullptr);
         a.free(w, nullptr);
@@ -478,8 +483,20 @@ static void test_alloc() {
         CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.live_pages());
         a.free(q, nullptr);
         CHECK(a.stats().free_runs == 1);                               // one run again, longer now
-        uint64_t r = a.malloc(400 * kSaPageBytes, nullptr, cfg);      // beyond the reserved room: a new segment
-        CHECK(r != 0 && a.stats().segments == 2 && a.stats().extensions == 1);
+        {   // a trimmed tail gives its slots back: the segment can grow into them again, from the pool
+            uint64_t keep = a.malloc(8 * kSaPageBytes, nullptr, cfg);  // front of the run stays live
+            CHECK(keep != 0);
+            a.trim(0, 0);                                              // the rest of the run is unmapped (whole chunks only)
+            const int creates_before = d.creates;
+            uint64_t big = a.malloc(40 * kSaPageBytes, nullptr, cfg);
+            CHECK(big != 0 && d.wrong_side_pages(big, 40 * kSaPageBytes) == 0);
+            if (d.model != 1) CHECK(d.creates - creates_before <= 12); // mostly pooled chunks
+            a.free(big, nullptr);
+            a.free(keep, nullptr);
+        }
+        const uint64_t ext_before = a.stats().extensions;
+        uint64_t r = a.malloc(5000 * kSaPageBytes, nullptr, cfg);     // beyond the reserved room: a new segment
+        CHECK(r != 0 && a.stats().segments == 2 && a.stats().extensions == ext_before);
         a.free(r, nullptr);
         a.release_unused();
         CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
