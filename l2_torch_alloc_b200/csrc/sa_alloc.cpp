@@ -110,15 +110,28 @@ void SaAllocator::erase_free(std::map<uint64_t, Run>::iterator it) {
     free_.erase(it);
 }
 
-// Adds a free run and merges it with free neighbours of the same segment.
+// Adds a free run and merges it with free neighbours of the same segment that were last used on
+// the same stream.  (Runs of different streams stay apart: a merged run would have to wait for
+// every stream that ever touched a part of it, and with few long segments such runs would soon
+// be the rule.  Each stream so keeps runs of its own, as in torch's caching allocator.)
 void SaAllocator::insert_free(uint64_t va, Run run) {
     auto merge = [](Run& into, const Run& other) {
         into.pages += other.pages;
         into.freed_seq = std::max(into.freed_seq, other.freed_seq);
-        if (other.mixed || other.stream != into.stream) into.mixed = true;
+        if (into.clean) { // the other one's user is the only one to wait for
+            into.stream = other.stream;
+            into.mixed = other.mixed;
+            into.clean = other.clean;
+        } else if (!other.clean && (other.mixed || other.stream != into.stream)) {
+            into.mixed = true;
+        }
+    };
+    auto same_user = [](const Run& a, const Run& b) {
+        return a.clean || b.clean || (a.stream == b.stream && !a.mixed && !b.mixed);
     };
     auto next = free_.lower_bound(va);
-    if (next != free_.end() && next->second.seg == run.seg && va + run.pages * kSaPageBytes == next->first) {
+    if (next != free_.end() && next->second.seg == run.seg && va + run.pages * kSaPageBytes == next->first &&
+        same_user(next->second, run)) {
         Run n = next->second;
         erase_free(next);
         merge(run, n);
@@ -126,7 +139,7 @@ void SaAllocator::insert_free(uint64_t va, Run run) {
     auto prev = free_.lower_bound(va);
     if (prev != free_.begin()) {
         --prev;
-        if (prev->second.seg == run.seg && prev->first + prev->second.pages * kSaPageBytes == va) {
+        if (prev->second.seg == run.seg && prev->first + prev->second.pages * kSaPageBytes == va && same_user(prev->second, run)) {
             Run p = prev->second;
             uint64_t pva = prev->first;
             erase_free(prev);
@@ -141,17 +154,20 @@ void SaAllocator::insert_free(uint64_t va, Run run) {
 }
 
 // Best fit: the shortest free run that can hold `pages` pages starting on side `phase`
-// (a run that starts on the other side needs one page more; that page stays free).
+// (a run that starts on the other side needs one page more; that page stays free).  Among the
+// shortest few, one last used on the asking stream is preferred: it needs no waiting.
 uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, void* stream) {
     auto& index = free_by_len_[compressed];
     auto it = index.lower_bound(pages);
     std::map<uint64_t, Run>::iterator pick = free_.end();
-    for (; it != index.end(); ++it) {
+    int looked = 0;
+    for (; it != index.end() && looked < 16; ++it) {
         const bool aligned = side_bit(it->second) == phase;
-        if (aligned || it->first >= pages + 1) {
-            pick = free_.find(it->second);
-            break;
-        }
+        if (!(aligned || it->first >= pages + 1)) continue;
+        auto cand = free_.find(it->second);
+        ++looked;
+        if (pick == free_.end()) pick = cand;
+        if (cand->second.clean || (!cand->second.mixed && cand->second.stream == stream)) { pick = cand; break; }
     }
     if (pick == free_.end()) return 0;
     const uint64_t run_va = pick->first;
@@ -171,7 +187,8 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
         insert_free(base + pages * kSaPageBytes, rest);
     }
     // work queued by the previous user(s) of these pages must be done before a different stream touches them
-    if (run.mixed) be_->device_sync();
+    if (run.clean) {}
+    else if (run.mixed) be_->device_sync();
     else if (run.stream != stream) be_->stream_sync(run.stream);
     Block b;
     b.pages = pages;
@@ -600,7 +617,8 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
             insert_free(best_va, head);
         }
         // work queued by the previous user(s) of the run must be done before a different stream touches it
-        if (run.mixed) be_->device_sync();
+        if (run.clean) {}
+        else if (run.mixed) be_->device_sync();
         else if (run.stream != stream) be_->stream_sync(run.stream);
         base = best_va + skip * kSaPageBytes;
     } else {
@@ -610,6 +628,7 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
             gap.seg = best;
             gap.freed_seq = ++seq_;
             gap.stream = stream;
+            gap.clean = true; // never used
             insert_free(end, gap);
         }
         base = end + lead * kSaPageBytes;
@@ -692,8 +711,29 @@ size_t SaAllocator::reclaimable_pages(uint64_t va, const Run& run) const {
 // If more than `start` bytes could be given back (free runs, less the pieces of chunks that reach
 // into live neighbours: those stay mapped whatever happens): unmaps free runs, least recently
 // freed first, until at most `end` bytes could still be given back.
+// After a device-wide synchronisation nobody's work is pending on any free run: neighbours
+// merge whatever stream they were last used on.
+void SaAllocator::merge_all_free_runs() {
+    std::vector<uint64_t> all;
+    all.reserve(free_.size());
+    for (auto& kv : free_) {
+        kv.second.clean = true;
+        kv.second.mixed = false;
+        all.push_back(kv.first);
+    }
+    for (uint64_t va : all) {
+        auto it = free_.find(va);
+        if (it == free_.end()) continue; // already swallowed by its predecessor
+        const Run r = it->second;
+        erase_free(it);
+        insert_free(va, r);
+    }
+}
+
 void SaAllocator::trim_locked(size_t start, size_t end) {
     if (cached_bytes_ <= start || cached_bytes_ == 0) return;
+    be_->device_sync(); // freed pages may still be in use by queued work
+    merge_all_free_runs();
     struct Cand { uint64_t seq, va; size_t pages; };
     std::vector<Cand> order;
     order.reserve(free_.size());
@@ -706,7 +746,6 @@ void SaAllocator::trim_locked(size_t start, size_t end) {
     }
     if (reclaimable == 0 || reclaimable <= start) return;
     std::sort(order.begin(), order.end(), [](const Cand& a, const Cand& b) { return a.seq < b.seq; });
-    be_->device_sync(); // freed pages may still be in use by queued work
     st_.trims++;
     for (auto& o : order) {
         if (reclaimable <= end) break;

@@ -130,6 +130,7 @@ private:
         uint64_t freed_seq = 0;
         void* stream = nullptr; // stream of the last user(s); mixed = several
         bool mixed = false;
+        bool clean = false;     // nobody's work is pending on these pages (never used, or the device was synchronised since)
     };
     struct Block {
         size_t pages = 0, requested = 0;
@@ -145,6 +146,7 @@ private:
     void erase_free(std::map<uint64_t, Run>::iterator it);
     void unmap_run(uint64_t va, const Run& run);
     void trim_locked(size_t start, size_t end);
+    void merge_all_free_runs();
     size_t reclaimable_pages(uint64_t va, const Run& run) const;
     void release_pools();
     int choose_phase(size_t bytes, size_t pages, bool compressed);

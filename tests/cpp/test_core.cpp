@@ -441,6 +441,30 @@ static void test_alloc() {
         a.free(p2, (void*)2);
         (void)p2;
     }
+    {   // free runs last used on different streams stay apart; a request prefers a run of its own stream
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t p1 = a.malloc(8 * kSaPageBytes, (void*)1, cfg);
+        uint64_t p2 = a.malloc(8 * kSaPageBytes, (void*)2, cfg);
+        CHECK(p1 && p2 && d.reservations.size() == 1 && p2 == p1 + 8 * kSaPageBytes); // side by side in one segment
+        a.free(p1, (void*)1);
+        a.free(p2, (void*)2);
+        CHECK(a.stats().free_runs == 2);                     // not merged: two streams
+        uint64_t q = a.malloc(8 * kSaPageBytes, (void*)2, cfg);
+        CHECK(q == p2 && d.stream_syncs == 0 && d.syncs == 0); // its own stream's run, although p1's comes first
+        a.free(q, (void*)2);
+        a.trim(1, 0);                                          // a device-wide wait makes every run anybody's
+        CHECK(a.stats().bytes_cached == 0 && d.syncs >= 1);
+        uint64_t r = a.malloc(16 * kSaPageBytes, (void*)3, cfg);
+        CHECK(r != 0 && d.stream_syncs == 0);
+        a.free(r, (void*)3);
+        uint64_t s1 = a.malloc(8 * kSaPageBytes, (void*)3, cfg), s2 = a.malloc(8 * kSaPageBytes, (void*)3, cfg);
+        a.free(s1, (void*)3);
+        a.free(s2, (void*)3);
+        CHECK(a.stats().free_runs == 1);                     // same stream: merged
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
+    }
     {   // trimming a run in the middle of a segment leaves the rest usable; the range is released with the last page
         FakeDriver d;
         SaAllocator a(&d, false);
@@ -585,6 +609,11 @@ static void test_alloc() {
                     (unsigned long long)st.trims, (unsigned long long)st.segments, (unsigned long long)st.free_runs);
         for (auto& l : live) a.free(l.first, nullptr);
         a.release_unused();
+        if (!(d.mappings.empty() && d.handles.empty() && d.reservations.empty())) {
+            SaAllocStats e = a.stats();
+            std::printf("left: %zu mappings, %zu handles, %zu reservations; cached %llu live %llu pool %llu+%llu runs %llu\n", d.mappings.size(), d.handles.size(),
+                        d.reservations.size(), (unsigned long long)e.bytes_cached, (unsigned long long)e.bytes_live, (unsigned long long)e.pages_pool[0], (unsigned long long)e.pages_pool[1], (unsigned long long)e.free_runs);
+        }
         CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
     std::printf("alloc: done\n");
