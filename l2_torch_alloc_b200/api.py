@@ -19,6 +19,8 @@ def _stream_ptr(stream) -> int:
         return 0
     if isinstance(stream, int):
         return stream
+    if isinstance(stream, ctypes.c_void_p):
+        return stream.value or 0
     return int(stream.cuda_stream)
 
 

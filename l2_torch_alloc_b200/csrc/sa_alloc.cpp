@@ -189,7 +189,7 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
     // work queued by the previous user(s) of these pages must be done before a different stream touches them
     if (run.clean) {}
     else if (run.mixed) be_->device_sync();
-    else if (run.stream != stream) be_->stream_sync(run.stream);
+    else if (run.stream != stream) be_->order_after(run.stream, stream);
     Block b;
     b.pages = pages;
     b.seg = run.seg;
@@ -619,7 +619,7 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
         // work queued by the previous user(s) of the run must be done before a different stream touches it
         if (run.clean) {}
         else if (run.mixed) be_->device_sync();
-        else if (run.stream != stream) be_->stream_sync(run.stream);
+        else if (run.stream != stream) be_->order_after(run.stream, stream);
         base = best_va + skip * kSaPageBytes;
     } else {
         if (lead) {

@@ -31,7 +31,7 @@
 //
 // Kept from the reference: 2 MiB granularity, bit 21 == side, same page-rounded size => same
 // start side (sideaware.cu:1082-1089), free never unmaps (:1254-1273), cross-stream reuse waits
-// for the previous user (:1209-1214), the out-of-memory ladder: unmap free memory above a
+// for the previous user (:1209-1214; on the device, through an event, where the reference blocks the host), the out-of-memory ladder: unmap free memory above a
 // threshold, unmap all of it, release all pooled pages (:1233-1252), cross-side fallback with a
 // one-time warning (:1137-1151).  Differences: per-device lock; address ranges are released
 // with the size they were reserved with (the reference: :1094 vs :896); a page mapped against
@@ -71,7 +71,8 @@ struct SaBackend {
     // side (0/1) of byte 0 of each of the `n` mapped, accessible pages at the addresses `vas`
     virtual int probe_pages(const uint64_t* vas, int n, uint8_t* sides, void* stream) = 0;
     virtual void device_sync() = 0;
-    virtual void stream_sync(void* stream) = 0;
+    // work queued on `later` from now on runs after everything queued on `earlier` so far (no host wait)
+    virtual void order_after(void* earlier, void* later) = 0;
 };
 
 struct SaAllocConfig {

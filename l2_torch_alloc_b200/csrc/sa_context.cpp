@@ -129,14 +129,24 @@ public:
         ScopedTime st(T_SYNC);
         cudaDeviceSynchronize();
     }
-    void stream_sync(void* stream) override {
+    // An event recorded on `earlier` now stands for all work queued there so far; `later` waits for it on
+    // the device.  Called under the allocator's lock, so one event per device is enough (a wait refers to
+    // the record that preceded it, recording again later does not change it).  If the stream that used
+    // the memory is gone, or anything else fails, the whole device is waited for instead.
+    void order_after(void* earlier, void* later) override {
         ScopedTime st(T_SYNC);
-        cudaStreamSynchronize((cudaStream_t)stream);
+        if (!order_event_ && cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming) != cudaSuccess) order_event_ = nullptr;
+        if (order_event_ && cudaEventRecord(order_event_, (cudaStream_t)earlier) == cudaSuccess &&
+            cudaStreamWaitEvent((cudaStream_t)later, order_event_, 0) == cudaSuccess)
+            return;
+        cudaGetLastError(); // the failed call's error must not stick to the caller's next launch
+        cudaDeviceSynchronize();
     }
 
 private:
     SaDevice* dev_;
     const SaDriver* d_;
+    cudaEvent_t order_event_ = nullptr;
 };
 
 std::mutex g_devices_mu;

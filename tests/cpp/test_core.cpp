@@ -269,7 +269,7 @@ struct FakeDriver : SaBackend {
         return 0;
     }
     void device_sync() override { ++syncs; }
-    void stream_sync(void*) override { ++stream_syncs; }
+    void order_after(void* earlier, void* later) override { CHECK(earlier != later); ++stream_syncs; }
 
     // pages of a live block: mapped, accessible, and on the side bit 21 of their address says
     int wrong_side_pages(uint64_t base, size_t bytes) {

@@ -151,3 +151,31 @@ def test_more_streams_than_one_block_of_rings(sa):
     for p in (src, mid, dst):
         sa.free(p)
     destroy_streams(streams)
+
+
+def test_block_reused_on_another_stream_waits_for_its_previous_user(sa):
+    """A block freed on stream A while A still has copies into it queued, then handed to stream B: B's
+    work on it must run after A's (the allocator orders the streams on the device, sideaware.cu:1209-1214
+    blocks the host instead).  B writes other bytes; they must be what is there in the end."""
+    dev = 0
+    n = 256 << 20
+    a_stream, b_stream = make_streams(2)
+    src1, _ = device_bytes(sa, n, 21)
+    src2, host2 = device_bytes(sa, n, 22)
+    ch.sync()
+    for attempt in range(3):
+        x = sa.malloc(n, a_stream)
+        for _ in range(24):                      # ~2 ms of copies into x queued on A
+            sa.lib.sideaware_memcpy(x, src1, n, dev, a_stream)
+        sa.free(x, a_stream)
+        y = sa.malloc(n, b_stream)
+        assert y == x, "the freed block is the best fit for an equal request"
+        sa.lib.sideaware_memcpy(y, src2, n, dev, b_stream)
+        ch.check(ch.cudart().cudaStreamSynchronize(b_stream), "cudaStreamSynchronize")
+        got = ch.d2h(y, n)
+        ch.sync()
+        assert np.array_equal(got, host2), f"attempt {attempt}: the other stream's queued copies ran after the new owner's"
+        sa.free(y, b_stream)
+    for p in (src1, src2):
+        sa.free(p)
+    destroy_streams([a_stream, b_stream])
