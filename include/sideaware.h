@@ -17,6 +17,9 @@
 
 #include <stddef.h>
 #include <stdint.h>
+#ifndef __cplusplus
+#include <stdbool.h>
+#endif
 
 #ifdef __cplusplus
 extern "C" {
@@ -162,6 +165,8 @@ size_t sideaware_chunk_sides(const void* ptr, size_t num_bytes, unsigned char* h
 int sideaware_verify_chunk_sides(const void* ptr, size_t num_bytes, int samples, unsigned seed);
 
 /* Counters of the current device, for tests and monitoring. */
+#ifndef SIDEAWARE_STATS_T
+#define SIDEAWARE_STATS_T
 typedef struct sideaware_stats_t {
     unsigned long long bytes_mapped_live;   /* side-aware blocks handed out */
     unsigned long long bytes_mapped_cached; /* freed but still mapped */
@@ -182,6 +187,7 @@ typedef struct sideaware_stats_t {
     unsigned long long handles_discarded;      /* handles given back because their pages' sides did not alternate */
     unsigned long long extensions;             /* blocks made of a segment's last free run plus newly mapped pages */
 } sideaware_stats_t;
+#endif
 void sideaware_get_stats(sideaware_stats_t* out);
 
 /* Host time (ns) and call counts the allocator has spent in driver calls since load, by kind:

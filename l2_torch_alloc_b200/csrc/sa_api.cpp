@@ -7,8 +7,10 @@
 
 #include "../../include/sideaware.h"
 #include "sa_context.hpp"
+#ifndef SIDEAWARE_ALLOC_ONLY
 #include "sa_jit.hpp"
 #include "sa_kernels.hpp"
+#endif
 
 #define SA_API extern "C" __attribute__((visibility("default")))
 
@@ -41,6 +43,7 @@ cudaError_t free_large(SaDevice* dev, void* ptr, cudaStream_t stream) {
     return cudaFreeAsync(ptr, stream);
 }
 
+#ifndef SIDEAWARE_ALLOC_ONLY
 bool check_launch_args(const char* what, size_t num_bytes, const void* const* ptrs, int n) {
     if (num_bytes % 16 != 0) {
         sa_set_error("%s: num_bytes (%zu) must be a multiple of 16", what, num_bytes);
@@ -53,6 +56,7 @@ bool check_launch_args(const char* what, size_t num_bytes, const void* const* pt
         }
     return true;
 }
+#endif
 
 } // namespace
 
@@ -146,6 +150,7 @@ SA_API void sideaware_free_auto(void* ptr, size_t size, int device, sideaware_st
     }
 }
 
+#ifndef SIDEAWARE_ALLOC_ONLY // the allocator-only build has no kernels and no functor compiler
 // ---------------------------------------------------------------------------
 // kernels
 // ---------------------------------------------------------------------------
@@ -345,6 +350,8 @@ SA_API int sideaware_compile_check(const char* header, int wide, char* log_out, 
 
 SA_API int sideaware_create_kernel(const char* header) { return sideaware_create_kernel_advanced(header, false, 4); }
 
+#endif // SIDEAWARE_ALLOC_ONLY
+
 // ---------------------------------------------------------------------------
 // configuration
 // ---------------------------------------------------------------------------
@@ -366,10 +373,13 @@ SA_API void sideaware_free_mapped_thresholds(size_t start_threshold, size_t end_
     sa_config().alloc.trim_start = start_threshold;
     sa_config().alloc.trim_end = end_threshold;
 }
+#ifndef SIDEAWARE_ALLOC_ONLY
 SA_API void sideaware_write_sass(const char* filename) {
     std::lock_guard<std::mutex> lock(sa_config().mu);
     sa_config().log_file = filename ? filename : "";
 }
+#endif
+#ifndef SIDEAWARE_ALLOC_ONLY
 SA_API void sideaware_set_placement(int mode) {
     if (mode < 0 || mode > 2) mode = 0;
     sa_config().placement.store(mode);
@@ -377,6 +387,7 @@ SA_API void sideaware_set_placement(int mode) {
 SA_API int sideaware_get_placement(void) { return sa_config().placement.load(); }
 SA_API void sideaware_set_memcpy_engine(int engine) { sa_config().memcpy_engine.store(engine == 0 ? 0 : 1); }
 SA_API int sideaware_get_memcpy_engine(void) { return sa_config().memcpy_engine.load(); }
+#endif
 
 // ---------------------------------------------------------------------------
 // queries
@@ -481,6 +492,7 @@ SA_API const char* sideaware_topology_json(void) {
     return dev ? dev->topo.json.c_str() : "{}";
 }
 
+#ifndef SIDEAWARE_ALLOC_ONLY
 // ---------------------------------------------------------------------------
 // memcpy without any device-memory allocation
 // ---------------------------------------------------------------------------
@@ -529,3 +541,4 @@ SA_API sideaware_status_t sideaware_memcpy_noalloc(void* out, const void* in, si
     if (e != cudaSuccess) sa_set_error("sideaware_memcpy_noalloc: %s", cudaGetErrorString(e));
     return e;
 }
+#endif // SIDEAWARE_ALLOC_ONLY

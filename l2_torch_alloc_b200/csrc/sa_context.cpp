@@ -5,7 +5,9 @@
 #include <cstdio>
 #include <cstring>
 
+#ifndef SIDEAWARE_ALLOC_ONLY
 #include "sa_jit.hpp"
+#endif
 
 // ---------------------------------------------------------------------------
 // errors
@@ -234,7 +236,9 @@ bool init_device(SaDevice* dev) {
     size_t free_bytes = 0, total_bytes = 0;
     cudaMemGetInfo(&free_bytes, &total_bytes);
     dev->alloc.reset(new SaAllocator(dev->backend.get(), dev->compression_supported, total_bytes));
+#ifndef SIDEAWARE_ALLOC_ONLY
     dev->jit = sa_jit_new_device_cache();
+#endif
     if (const char* dump = std::getenv("SIDEAWARE_DUMP_TOPOLOGY")) {
         std::string path = std::string(dump) + "." + std::to_string(dev->id) + ".json";
         if (FILE* f = std::fopen(path.c_str(), "w")) { std::fputs(dev->topo.json.c_str(), f); std::fclose(f); }

@@ -140,3 +140,58 @@ int main(int argc, char**) {
     subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src),
                            "-L", libdir, "-l:sideaware.so", f"-Wl,-rpath,{libdir}", "-o", str(exe)])
     assert subprocess.run([str(exe)]).returncode == 0
+
+
+# ---------------------------------------------------------------------------
+# the allocator-only library (counterpart of the reference's sideaware_alloc.cu)
+# ---------------------------------------------------------------------------
+ALLOC_ONLY_REFERENCE_SYMBOLS = """
+sideaware_malloc_async sideaware_free_async sideaware_malloc sideaware_free sideaware_release_unused
+sideaware_compression sideaware_prealloc_config sideaware_free_mapped_thresholds sideaware_fill_side_index
+sideaware_gpu_side_index sideaware_cpu_side_index sideaware_sm_side_summary sideaware_num_sms
+sideaware_num_sm_side0 sideaware_num_sm_side1 sideaware_min_sm_per_side sideaware_hash_mask
+""".split()  # extern "C" block of sideaware_alloc.cu:692-762
+
+
+def alloc_header_symbols():
+    text = open(os.path.join(ROOT, "include", "sideaware_alloc.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sideaware_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_allocator_only_library_exports_what_its_header_declares():
+    import ctypes
+    import subprocess
+    path = build.build(alloc_only=True)
+    lib = ctypes.CDLL(path)  # loads without a GPU and without NVRTC
+    declared = alloc_header_symbols()
+    assert set(ALLOC_ONLY_REFERENCE_SYMBOLS) <= set(declared)
+    assert set(declared) <= set(header_symbols()), "the two headers must declare the same functions under the same names"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in sideaware_alloc.h but not exported by sideaware_alloc.so"
+    exported = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
+    exported = sorted(set(re.findall(r" T (sideaware_[a-z0-9_]+)", exported)))
+    assert exported == declared, "exports and header disagree"
+    for absent in ("sideaware_elementwise", "sideaware_memcpy", "sideaware_create_kernel", "sideaware_rope_forward"):
+        assert absent not in exported
+    lib.sideaware_last_error.restype = ctypes.c_char_p
+    lib.sideaware_malloc_auto.restype = ctypes.c_void_p
+    lib.sideaware_malloc_auto.argtypes = [ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+    import torch
+    if not torch.cuda.is_available():
+        assert not lib.sideaware_malloc_auto(16 << 20, 0, None)  # loud failure, no fallback
+        assert b"CUDA" in lib.sideaware_last_error() or b"device" in lib.sideaware_last_error()
+
+
+def test_headers_compile_as_c_and_together_as_cxx(tmp_path):
+    import subprocess
+    inc = os.path.join(ROOT, "include")
+    c_file = tmp_path / "only_alloc.c"
+    c_file.write_text('#include "sideaware_alloc.h"\nint main(void) { sideaware_stats_t s; (void)s; return sideaware_num_sms() < 0; }\n')
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", inc, "-c", str(c_file), "-o", str(tmp_path / "a.o")], check=True)
+    c_full = tmp_path / "full.c"
+    c_full.write_text('#include "sideaware.h"\nint main(void) { return sideaware_num_sms() < 0; }\n')
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", inc, "-c", str(c_full), "-o", str(tmp_path / "c.o")], check=True)
+    cxx_file = tmp_path / "both.cpp"
+    cxx_file.write_text('#include "sideaware.h"\n#include "sideaware_alloc.h"\n#include "sideaware.h"\nint main() { sideaware_stats_t s; (void)s; return 0; }\n')
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", inc, "-c", str(cxx_file), "-o", str(tmp_path / "b.o")], check=True)

@@ -208,3 +208,43 @@ def test_compressible_memory_option(sa):
     sa.free(c)
     sa.free(plain)
     assert sa.error_count() == errors_before, sa.last_error()
+
+
+def test_allocator_only_library_places_pages_by_side():
+    """sideaware_alloc.so (no kernels, no functor compiler) in a process of its own: blocks are 2 MiB aligned, equal
+    sizes start on the same side, re-measured chunks are on the side the address predicts."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib_path = os.path.join(root, "l2_torch_alloc_b200", "sideaware_alloc.so")
+    if not os.path.exists(lib_path):
+        from l2_torch_alloc_b200 import build
+        build.build(alloc_only=True)
+    code = f"""
+import ctypes
+lib = ctypes.CDLL({lib_path!r})
+lib.sideaware_malloc_async.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t, ctypes.c_void_p]
+lib.sideaware_free_async.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+lib.sideaware_verify_chunk_sides.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_uint]
+lib.sideaware_release_unused.restype = ctypes.c_size_t
+lib.sideaware_last_error.restype = ctypes.c_char_p
+n = 192 << 20
+ptrs = []
+for _ in range(2):
+    p = ctypes.c_void_p()
+    rc = lib.sideaware_malloc_async(ctypes.byref(p), n, None)
+    assert rc == 0 and p.value and p.value % (2 << 20) == 0, (rc, lib.sideaware_last_error())
+    ptrs.append(p.value)
+assert (ptrs[0] >> 21) & 1 == (ptrs[1] >> 21) & 1
+for p in ptrs:
+    bad = lib.sideaware_verify_chunk_sides(p, n, 512, 5)
+    assert 0 <= bad <= 8, bad
+assert lib.sideaware_num_sms() >= 100 and (lib.sideaware_hash_mask() >> 21) & 1
+for p in ptrs:
+    assert lib.sideaware_free_async(p, None) == 0
+assert lib.sideaware_release_unused() >= 2 * n
+print("ALLOC-ONLY-OK", lib.sideaware_num_sm_side0(), lib.sideaware_num_sm_side1())
+"""
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, cwd=root)
+    assert "ALLOC-ONLY-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
