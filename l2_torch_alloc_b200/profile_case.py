@@ -4,6 +4,8 @@
     python -m l2_torch_alloc_b200.profile_case rope     [--batch 2]  [--reps 4]
     python -m l2_torch_alloc_b200.profile_case functor  [--mib 256] [--reps 4]
     python -m l2_torch_alloc_b200.profile_case functor-jit [--mib 256] [--reps 4]   (the same functor through NVRTC)
+    python -m l2_torch_alloc_b200.profile_case growth   [--mib 1024] [--reps 3]     (no kernel of interest: host time of
+                                                         first-touch allocation and the driver calls it took, as JSON)
 
 Each case touches more than the 126 MB L2 but well under 2 GB of device memory and
 launches the kernel of interest a handful of times, so a multi-pass capture ends by itself.
@@ -19,7 +21,7 @@ import l2_torch_alloc_b200 as pkg
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["memcpy", "rope", "functor", "functor-jit"])
+    ap.add_argument("case", choices=["memcpy", "rope", "functor", "functor-jit", "growth"])
     ap.add_argument("--mib", type=int, default=256)
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--reps", type=int, default=4)
@@ -30,7 +32,33 @@ def main():
     sa.set_placement(args.placement)
     sa.lib.sideaware_set_memcpy_engine(args.engine)
     torch.cuda.set_device(0)
-    if args.case == "memcpy":
+    if args.case == "growth":
+        import json
+        import time
+        n = args.mib << 20
+        out = {"block_mib": args.mib, "blocks": []}
+        ptrs = []
+        for _ in range(args.reps):
+            before = sa.driver_call_times()
+            t0 = time.perf_counter()
+            p = sa.malloc(n)
+            dt = time.perf_counter() - t0
+            after = sa.driver_call_times()
+            ptrs.append(p)
+            out["blocks"].append({"ms": round(dt * 1e3, 2), "us_per_2MiB_page": round(dt * 1e6 / (n / (2 << 20)), 1),
+                                  "chunks_not_on_predicted_side_of_512": sa.verify_chunk_sides(p, n, 512, 1),
+                                  "driver_calls": {k: {"calls": after[k]["calls"] - before[k]["calls"],
+                                                       "ms": round(after[k]["ms"] - before[k]["ms"], 2)} for k in after}})
+        st = sa.stats()
+        out["stats"] = {k: st[k] for k in ("pages_created", "handles_created", "handles_discarded", "cross_side_pages", "extensions")}
+        t0 = time.perf_counter()
+        for p in ptrs:
+            sa.free(p)
+        q = sa.malloc(n)  # served from what is mapped
+        out["malloc_after_free_us"] = round((time.perf_counter() - t0) * 1e6, 1)
+        sa.free(q)
+        print("GROWTH", json.dumps(out))
+    elif args.case == "memcpy":
         n = args.mib << 20
         seed = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
         a, b = sa.malloc(n), sa.malloc(n)
