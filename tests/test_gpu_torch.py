@@ -73,3 +73,23 @@ print("COMPILED-ROPE-OK")
 """
     r = run_script(["-c", code])
     assert "COMPILED-ROPE-OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_training_steps_match_torchs_own_allocator():
+    """Six optimizer steps of a small MLP under the pluggable allocator give the losses torch's own allocator gives."""
+    out = {}
+    for mode in ("native", "sideaware"):
+        r = run_script([os.path.join(ROOT, "tests", "training_equivalence_script.py"), mode])
+        lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+        assert lines, r.stdout[-3000:] + r.stderr[-3000:]
+        out[mode] = json.loads(lines[-1][7:])
+    a = [float.fromhex(v) for v in out["native"]["losses"]]
+    b = [float.fromhex(v) for v in out["sideaware"]["losses"]]
+    print("losses native   ", a)
+    print("losses sideaware", b)
+    assert len(a) == len(b) == 6
+    for u, v in zip(a, b):
+        assert abs(u - v) <= 1e-6 * abs(u), (a, b)  # same kernels on the same data: equal up to cuBLAS's choice of algorithm
+    st = out["sideaware"]["stats"]
+    assert out["sideaware"]["errors"] == 0 and st["large_allocs"] >= 10 and st["cross_side_pages"] == 0
+    assert st["reuse_hits"] >= st["large_allocs"] // 2, "after the first step most blocks come from mapped runs"
