@@ -85,6 +85,7 @@ def test_training_steps_match_torchs_own_allocator():
         out[mode] = json.loads(lines[-1][7:])
     a = [float.fromhex(v) for v in out["native"]["losses"]]
     b = [float.fromhex(v) for v in out["sideaware"]["losses"]]
+    print("ms per step: native", out["native"]["ms_per_step"], "sideaware", out["sideaware"]["ms_per_step"])
     print("losses native   ", a)
     print("losses sideaware", b)
     assert len(a) == len(b) == 6
@@ -93,3 +94,4 @@ def test_training_steps_match_torchs_own_allocator():
     st = out["sideaware"]["stats"]
     assert out["sideaware"]["errors"] == 0 and st["large_allocs"] >= 10 and st["cross_side_pages"] == 0
     assert st["reuse_hits"] >= st["large_allocs"] // 2, "after the first step most blocks come from mapped runs"
+    assert out["sideaware"]["ms_per_step"] <= 1.25 * out["native"]["ms_per_step"] + 1.0, "the allocator must not slow the steady state down"

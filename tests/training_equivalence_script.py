@@ -33,9 +33,23 @@ def main():
         opt.step()
         losses.append(float(loss.item()).hex())
     torch.cuda.synchronize()
+    # steady state: the same step repeated, every allocation of a size seen before
+    import time
+    t0 = time.perf_counter()
+    timed = 20
+    for _ in range(timed):
+        x = torch.randn(batch, width, device="cuda", generator=gen)
+        y = torch.randn(batch, width, device="cuda", generator=gen)
+        loss = torch.nn.functional.mse_loss(model(x), y)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+    torch.cuda.synchronize()
+    ms_per_step = (time.perf_counter() - t0) / timed * 1e3
     if sa is not None:
         stats = sa.stats()
-    print("RESULT " + json.dumps({"mode": mode, "losses": losses, "stats": stats, "errors": sa.error_count() if sa else 0}))
+    print("RESULT " + json.dumps({"mode": mode, "losses": losses, "ms_per_step": ms_per_step, "stats": stats,
+                                  "errors": sa.error_count() if sa else 0}))
     return 0
 
 
