@@ -179,3 +179,26 @@ def test_block_reused_on_another_stream_waits_for_its_previous_user(sa):
     for p in (src1, src2):
         sa.free(p)
     destroy_streams([a_stream, b_stream])
+
+
+def test_more_streams_than_rings_can_ever_be_made(sa):
+    """1 100 streams, each used once: beyond 1 024 stream handles the rings are handed out afresh (after a
+    device-wide wait, so no counter is in use).  Results stay exact and nothing is recorded as an error."""
+    dev = 0
+    errors_before = sa.error_count()
+    n_streams = 1100
+    piece = 64 << 10
+    streams = make_streams(n_streams)
+    src, host = device_bytes(sa, piece * n_streams, 6)
+    dst = sa.malloc(piece * n_streams)
+    ch.memset(dst, 0, piece * n_streams)
+    ch.sync()
+    for k, s in enumerate(streams):
+        sa.lib.sideaware_memcpy(dst + k * piece, src + k * piece, piece, dev, s)
+    ch.sync()
+    assert sa.error_count() == errors_before, sa.last_error()
+    assert np.array_equal(ch.d2h(dst, piece * n_streams), host)
+    assert sa.stats()["kernel_wait_timeouts"] == 0
+    for p in (src, dst):
+        sa.free(p)
+    destroy_streams(streams)
