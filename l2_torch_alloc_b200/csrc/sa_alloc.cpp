@@ -559,7 +559,7 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
 uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* stream) {
     Segment* best = nullptr;
     uint64_t best_va = 0;
-    size_t best_have = 0, best_room = 0;
+    size_t best_have = 0, best_room = 0, best_lead = 0;
     for (auto& sp : segments_) {
         Segment* seg = sp.get();
         if (seg->compressed != compressed || seg->num_pages >= seg->capacity) continue;
@@ -581,11 +581,13 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
         const size_t lead = have ? 0 : (side_bit(end) == phase ? 0 : 1);
         if (seg->num_pages + lead + (pages - have) > seg->capacity) continue;
         const size_t room = seg->capacity - seg->num_pages;
-        if (!best || have > best_have || (have == best_have && room > best_room)) {
+        // most pages already there; then no page wasted on getting the side right; then most room left
+        if (!best || have > best_have || (have == best_have && (lead < best_lead || (lead == best_lead && room > best_room)))) {
             best = seg;
             best_va = run_va;
             best_have = have;
             best_room = room;
+            best_lead = lead;
         }
     }
     if (!best) return 0;
