@@ -186,6 +186,7 @@ typedef struct sideaware_stats_t {
     unsigned long long handles_created;        /* cuMemCreate calls; pages_created counts the 2 MiB pages they hold */
     unsigned long long handles_discarded;      /* handles given back because their pages' sides did not alternate */
     unsigned long long extensions;             /* blocks made of a segment's last free run plus newly mapped pages */
+    unsigned long long hole_refills;           /* blocks mapped into a hole that a trim had left inside a segment */
 } sideaware_stats_t;
 #endif
 void sideaware_get_stats(sideaware_stats_t* out);

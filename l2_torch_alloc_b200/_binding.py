@@ -21,7 +21,7 @@ class Stats(ctypes.Structure):
         "bytes_mapped_live", "bytes_mapped_cached", "pages_pool_side0", "pages_pool_side1", "pages_created",
         "cross_side_pages", "reuse_hits", "large_allocs", "small_allocs", "trims", "jit_compiles",
         "kernel_launches", "probe_confidence_ppm", "hash_validation_errors", "kernel_wait_timeouts",
-        "handles_created", "handles_discarded", "extensions")]
+        "handles_created", "handles_discarded", "extensions", "hole_refills")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}

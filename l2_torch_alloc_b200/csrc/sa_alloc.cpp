@@ -645,10 +645,47 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
     return base;
 }
 
+// A stretch of slots that a trim left unmapped in the middle of a segment, long enough for the
+// block (best fit over all segments): the block goes there, next to its old neighbours, instead
+// of taking new address space.  A segment has such holes exactly when it maps fewer pages than it has slots.
+uint64_t SaAllocator::refill(size_t pages, int phase, bool compressed, void* stream) {
+    Segment* best = nullptr;
+    size_t best_start = 0, best_len = (size_t)-1;
+    for (auto& sp : segments_) {
+        Segment* seg = sp.get();
+        if (seg->compressed != compressed || seg->num_pages - seg->mapped_pages < pages) continue;
+        size_t i = 0;
+        while (i < seg->num_pages) {
+            if (seg->pages[i].handle) { ++i; continue; }
+            size_t e = i;
+            while (e < seg->num_pages && !seg->pages[e].handle) ++e; // hole [i, e)
+            const size_t start = i + (side_bit(seg->base + i * kSaPageBytes) == phase ? 0 : 1);
+            if (start + pages <= e && e - i < best_len) {
+                best = seg;
+                best_start = start;
+                best_len = e - i;
+            }
+            i = e;
+        }
+    }
+    if (!best) return 0;
+    if (!map_slots(best, best_start, best_start + pages, stream)) return 0;
+    best->mapped_pages += pages;
+    const uint64_t base = best->base + best_start * kSaPageBytes;
+    Block b;
+    b.pages = pages;
+    b.seg = best;
+    b.stream = stream;
+    live_.emplace(base, b);
+    live_bytes_ += pages * kSaPageBytes;
+    st_.hole_refills++;
+    return base;
+}
+
 // Unmaps what can be unmapped of a free run (already removed from the free indices) and returns
 // it to the pools.  A mapping can only be undone as a whole, so pages of chunks that reach beyond
-// the run stay mapped and go back into the free indices.  Holes stay reserved until the whole
-// segment is unmapped.
+// the run stay mapped and go back into the free indices.  Holes stay reserved (refill() uses them
+// again) until the whole segment is unmapped.
 void SaAllocator::unmap_run(uint64_t va, const Run& run) {
     Segment* seg = run.seg;
     const size_t first = (size_t)((va - seg->base) / kSaPageBytes), last = first + run.pages;
@@ -808,7 +845,8 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
     }
     // 2..4) the ladder of sideaware.cu:1233-1252: unmap free memory above the threshold, unmap
     // all of it, give all pooled pages back to the driver; try to grow the mapped set after each.
-    // Growing: a free run at the end of a segment plus as many new pages as are missing, else a new segment.
+    // Growing: into a hole an earlier trim left, else behind the last page of a segment (using the free run
+    // there, if any), else a new segment.
     for (int step = 0; step < 3; ++step) {
         if (step == 0) trim_locked(cfg.trim_start, cfg.trim_end);
         else if (step == 1) trim_locked(0, 0);
@@ -817,7 +855,8 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
             release_pools();
             be_->device_sync();
         }
-        p = step == 0 ? extend(pages, phase, compressed, stream) : 0;
+        p = refill(pages, phase, compressed, stream);
+        if (!p && step == 0) p = extend(pages, phase, compressed, stream);
         if (!p) p = grow(pages, phase, compressed, stream, cfg);
         if (p) {
             live_[p].requested = size;

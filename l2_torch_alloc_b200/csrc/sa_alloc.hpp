@@ -90,6 +90,7 @@ struct SaAllocStats {
     uint64_t handles_created = 0;   // cuMemCreate calls (pages_created counts their pages)
     uint64_t handles_discarded = 0; // created, measured, found unusable (pages do not alternate), given back
     uint64_t extensions = 0;        // blocks made of a segment's last free run plus newly mapped pages
+    uint64_t hole_refills = 0;      // blocks mapped into a hole that a trim had left inside a segment
 };
 
 class SaAllocator {
@@ -142,6 +143,7 @@ private:
     uint64_t take_from_free(size_t pages, int phase, bool compressed, void* stream);
     uint64_t grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg);
     uint64_t extend(size_t pages, int phase, bool compressed, void* stream);
+    uint64_t refill(size_t pages, int phase, bool compressed, void* stream);
     bool map_slots(Segment* seg, size_t lo, size_t hi, void* stream);
     void insert_free(uint64_t va, Run run);
     void erase_free(std::map<uint64_t, Run>::iterator it);

@@ -473,6 +473,7 @@ SA_API void sideaware_get_stats(sideaware_stats_t* out) {
     out->handles_created = st.handles_created;
     out->handles_discarded = st.handles_discarded;
     out->extensions = st.extensions;
+    out->hole_refills = st.hole_refills;
     out->jit_compiles = dev->jit_compiles.load();
     out->kernel_launches = dev->launches.load();
     out->probe_confidence_ppm = (unsigned long long)(dev->topo.confidence > 0 ? dev->topo.confidence * 1e6 : 0);

@@ -481,8 +481,9 @@ static void test_alloc() {
         CHECK(d.mappings.size() == 20 + st.bytes_cached / kSaPageBytes);
         CHECK(st.pages_pool[0] + st.pages_pool[1] + d.mappings.size() == d.live_pages());
         CHECK(d.wrong_side_pages(x, 10 * kSaPageBytes) == 0 && d.wrong_side_pages(z, 10 * kSaPageBytes) == 0);
-        uint64_t w = a.malloc(30 * kSaPageBytes, nullptr, cfg); // the hole is not reused: the block goes behind z, into the room reserved with the segment
-        CHECK(w != 0 && w != y && w > z && d.wrong_side_pages(w, 30 * kSaPageBytes) == 0 && d.reservations.size() == 1);
+        uint64_t w = a.malloc(30 * kSaPageBytes, nullptr, cfg); // into the hole if it is long enough, else behind z; never a new address range
+        CHECK(w != 0 && d.wrong_side_pages(w, 30 * kSaPageBytes) == 0 && d.reservations.size() == 1);
+        CHECK(d.wrong_side_pages(x, 10 * kSaPageBytes) == 0 && d.wrong_side_pages(z, 10 * kSaPageBytes) == 0);
         a.free(x, nullptr);
         a.free(z, nullptr);
         a.free(w, nullptr);
@@ -547,6 +548,31 @@ static void test_alloc() {
                 a.release_unused();
                 CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
             }
+    }
+    {   // a hole that a trim left inside a segment is used again, from the pool, without new address space
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        uint64_t x = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        uint64_t y = a.malloc(60 * kSaPageBytes, nullptr, cfg);
+        uint64_t z = a.malloc(10 * kSaPageBytes, nullptr, cfg);
+        CHECK(x && y && z && d.reservations.size() == 1);
+        a.free(y, nullptr);
+        a.trim(0, 0);
+        const size_t mapped_after_trim = d.mappings.size();
+        CHECK(mapped_after_trim < 80 && mapped_after_trim >= 20);
+        const int creates_before = d.creates;
+        uint64_t w = a.malloc(30 * kSaPageBytes, nullptr, cfg);
+        SaAllocStats st = a.stats();
+        CHECK(w != 0 && w > x && w < z && d.wrong_side_pages(w, 30 * kSaPageBytes) == 0); // between its old neighbours
+        CHECK(st.hole_refills == 1 && d.reservations.size() == 1);
+        if (d.model != 1) CHECK(d.creates - creates_before <= 4);                          // from the pool
+        CHECK(st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes == d.live_pages());
+        CHECK(d.mappings.size() == (st.bytes_live + st.bytes_cached) / kSaPageBytes);
+        a.free(w, nullptr);
+        a.free(x, nullptr);
+        a.free(z, nullptr);
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
     }
     {   // skewed physical side distribution still yields correctly placed blocks
         FakeDriver d;
