@@ -85,3 +85,51 @@ __device__ bool indexing(size_type vec_idx, int n, size_type &idx_i0, size_type 
     return in_row >= rope_rotated * rope_half;
 }}
 """
+
+
+def mxfp8_quantize_bf16() -> str:
+    """bf16 -> MXFP8 (OCP Microscaling Formats v1.0: blocks of 32 elements, elements FP8 E4M3, one shared
+    power-of-two scale per block stored as E8M0), the use the reference names for custom vector functions
+    (sideaware.cu:81-83).  out0 = the E4M3 bytes, the sideband array receives one scale byte per block
+    (pass it as a uint8 tensor viewed as int32).  A lane holds 8 elements, so the block maximum is taken
+    over the four lanes of a quad; the quad shuffles only if all four lanes are in this call together
+    (always, for an element count that is a multiple of 32 in a 64-byte-aligned array), otherwise each lane
+    scales by its own eight elements, so no lane can ever wait for one that does not come.
+    Scale: 2^(floor(log2(amax)) - 8), 8 being the largest E4M3 exponent; elements are rounded to nearest
+    even and saturate at +-448.  A block of zeros gets the smallest scale (byte 0); bf16 subnormals count as zero
+    (functor kernels are compiled with flush-to-zero)."""
+    return """
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+typedef __nv_fp8_e4m3 o0;
+typedef __nv_bfloat16 i0;
+struct unused {};
+typedef unused o1, o2, o3, i1, i2, i3;
+constexpr bool reverse_order = false;
+constexpr bool input_evict[4] = {1, 0, 0, 0};
+#define CUSTOM_VECTOR_OP
+__device__ void vector_op(size_type vec_idx, int n, o0 *out0, o1 *out1, o2 *out2, o3 *out3,
+                          const i0 *in0, const i1 *in1, const i2 *in2, const i3 *in3, int *mem, int val) {
+    float v[8];
+    float amax = 0.0f;
+    for (int e = 0; e < 8; e++) {
+        v[e] = e < n ? __bfloat162float(in0[e]) : 0.0f;
+        amax = fmaxf(amax, fabsf(v[e]));
+    }
+    const unsigned lane = threadIdx.x & 31u;
+    const unsigned quad = 0xFu << (lane & ~3u);
+    if ((__activemask() & quad) == quad) {
+        amax = fmaxf(amax, __shfl_xor_sync(quad, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(quad, amax, 2));
+    }
+    // floor(log2(amax)) is the exponent field of the float (bf16 values are never fp32 subnormals
+    // except bf16 subnormals, whose field is 0: they get the smallest scale, like zero)
+    int shared = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 8;
+    if (shared < -127) shared = -127;
+    // multiply by 2^-shared in two exact steps (2^127 and beyond are not floats)
+    const int h = (-shared) / 2, r = (-shared) - h;
+    const float s1 = __uint_as_float((unsigned)(127 + h) << 23), s2 = __uint_as_float((unsigned)(127 + r) << 23);
+    for (int e = 0; e < n; e++) out0[e] = __nv_fp8_e4m3(__fmul_rn(__fmul_rn(v[e], s1), s2));
+    if ((lane & 3u) == 0u) ((unsigned char*)mem)[vec_idx >> 2] = (unsigned char)(shared + 127);
+}
+"""

@@ -192,3 +192,46 @@ def ulp_diff_bf16(a_u16: np.ndarray, b_u16: np.ndarray) -> np.ndarray:
         u = u.astype(np.int32)
         return np.where(u & 0x8000, 0x8000 - u, u)
     return np.abs(key(a_u16) - key(b_u16))
+
+
+def f64_to_e4m3_bytes(x: np.ndarray) -> np.ndarray:
+    """FP8 E4M3 (the "fn" flavour of the OCP 8-bit floating point specification: bias 7, no infinities, largest
+    finite value 448) from exact values, round to nearest even, saturating: what a conversion with the
+    saturate-to-finite option produces for finite inputs."""
+    x = np.asarray(x, dtype=np.float64)
+    sign = np.signbit(x).astype(np.uint8) << 7
+    a = np.abs(x)
+    out = np.zeros(a.shape, dtype=np.uint8)
+    normal = a >= 2.0 ** -6
+    # subnormals and zero: multiples of 2^-9; rounding up to 8 gives the smallest normal, whose bit pattern is 8 as well
+    out[~normal] = np.rint(a[~normal] * 2.0 ** 9).astype(np.uint8)
+    an = a[normal]
+    e = np.floor(np.log2(an)).astype(np.int64)
+    e = np.where(an < 2.0 ** e, e - 1, e)          # guard against log2 rounding up at powers of two
+    e = np.where(an >= 2.0 ** (e + 1), e + 1, e)
+    r = np.rint(an / 2.0 ** (e - 3)).astype(np.int64)  # 8..16
+    carry = r == 16
+    e = np.where(carry, e + 1, e)
+    r = np.where(carry, 8, r)
+    too_big = (e > 8) | ((e == 8) & (r > 14))
+    e = np.where(too_big, 8, e)
+    r = np.where(too_big, 14, r)
+    out[normal] = (((e + 7) << 3) | (r - 8)).astype(np.uint8)
+    return out | sign
+
+
+def mxfp8_quantize_bf16(x_u16: np.ndarray):
+    """bf16 -> MXFP8 restated from the OCP Microscaling Formats specification v1.0: blocks of 32 elements, one
+    shared scale 2^(floor(log2(max |v|)) - 8) per block stored as E8M0 (exponent + 127; 8 is the largest E4M3
+    exponent), elements v / scale in E4M3.  The block maximum's exponent is read from its float exponent field,
+    so an all-zero block gives the smallest scale (2^-127, byte 0).  Returns (element bytes, scale bytes).
+    The reference only names this use (sideaware.cu:81-83); there is no reference implementation to compare with."""
+    v = bf16_to_f32(np.asarray(x_u16).reshape(-1)).reshape(-1, 32).copy()
+    # functor kernels are built with flush-to-zero (-use_fast_math, as in the reference, sideaware.cu:535):
+    # bf16 subnormals, which are float subnormals too, count as zero
+    v[((v.view(np.uint32) >> 23) & 0xFF) == 0] = 0.0
+    amax = np.abs(v).max(axis=1)
+    field = (amax.astype(np.float32).view(np.uint32) >> 23) & 0xFF
+    shared = np.maximum(field.astype(np.int64) - 127 - 8, -127)
+    scaled = np.ldexp(v.astype(np.float64), (-shared)[:, None])
+    return f64_to_e4m3_bytes(scaled).reshape(-1), (shared + 127).astype(np.uint8)

@@ -139,3 +139,37 @@ def test_custom_index_function_broadcast_and_skip(sa):
     keep = ((vec // 64) % 5) == 4
     want[keep] = x.view(-1, 4)[keep]
     assert torch.equal(out.view(-1, 4), want)
+
+
+def test_mxfp8_quantize_matches_restatement(sa):
+    """bf16 -> MXFP8 (blocks of 32, E4M3 elements, E8M0 scales in the sideband array): the use the reference names
+    for custom vector functions (sideaware.cu:81-83).  Element bytes and scale bytes equal the numpy restatement of
+    the OCP Microscaling v1.0 rules bit for bit, over magnitudes from bf16 subnormals to 3e38, zero blocks included."""
+    import numpy as np
+    import torch
+    from oracle import oracle
+    from l2_torch_alloc_b200 import functors
+    blocks = (1 << 17) + 37
+    n = blocks * 32
+    rng = np.random.default_rng(0xB200 + 8)
+    x = rng.standard_normal((blocks, 32)).astype(np.float32)
+    x *= np.exp2(rng.integers(-60, 60, size=(blocks, 1))).astype(np.float32)
+    x[5] = 0.0                                   # a block of zeros
+    x[6] = 3.0e38 * np.sign(x[6] + 0.5)          # near the top of the range
+    x[7] = 1.0e-40                               # bf16 subnormals
+    x[8, :] = 0.0
+    x[8, 3] = -448.0 * 2.0 ** 10                 # one element carries the block
+    x_u16 = oracle.f32_to_bf16(x.reshape(-1))
+    want_el, want_sc = oracle.mxfp8_quantize_bf16(x_u16)
+    xin = torch.from_numpy(x_u16.view(np.int16)).cuda().view(torch.bfloat16)
+    out = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    scales = torch.full(((blocks + 3) // 4 * 4,), 0xEE, dtype=torch.uint8, device="cuda")
+    kid = sa.create_kernel(functors.mxfp8_quantize_bf16())
+    sa.elementwise(kid, out, None, None, None, xin, None, None, None, scales.view(torch.int32), 0)
+    torch.cuda.synchronize()
+    got_el = out.cpu().numpy()
+    got_sc = scales.cpu().numpy()
+    assert np.array_equal(got_sc[:blocks], want_sc), np.nonzero(got_sc[:blocks] != want_sc)[0][:10]
+    assert (got_sc[blocks:] == 0xEE).all(), "no scale byte is written past the last block"
+    bad = np.nonzero(got_el != want_el)[0]
+    assert bad.size == 0, (bad[:10], got_el[bad[:10]], want_el[bad[:10]])

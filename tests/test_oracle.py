@@ -99,3 +99,17 @@ def test_memcpy_mt_is_exact():
         dst = np.zeros_like(src)
         oracle.lib().oracle_memcpy_mt(dst.ctypes.data, src.ctypes.data, src.size, threads)
         assert np.array_equal(dst, src)
+
+
+def test_e4m3_restatement_known_values():
+    """Known encodings of FP8 E4M3 (bias 7, largest finite 448, smallest subnormal 2^-9)."""
+    vals = [0.0, -0.0, 1.0, -1.0, 448.0, 1e9, -1e9, 2.0 ** -9, 2.0 ** -10, 2.0 ** -10 * 1.0001, 2.0 ** -6, 1.0625, 1.1875, 464.0, 17.0, 0.875]
+    want = [0x00, 0x80, 0x38, 0xB8, 0x7E, 0x7E, 0xFE, 0x01, 0x00, 0x01, 0x08, 0x38, 0x3A, 0x7E, 0x58, 0x36]
+    got = oracle.f64_to_e4m3_bytes(np.array(vals))
+    assert [int(g) for g in got] == want
+    # 1.0625 is halfway between 1.0 and 1.125: ties go to the even mantissa (1.0); 1.1875 between 1.125 and 1.25 -> 1.25
+    x = np.zeros(64, dtype=np.float32)
+    x[:32] = 3.0      # amax 3 -> floor(log2) = 1 -> shared exponent -7 -> elements 3 * 2^7 = 384 = 1.5 * 2^8
+    x[32:] = 0.0
+    el, sc = oracle.mxfp8_quantize_bf16(oracle.f32_to_bf16(x))
+    assert sc.tolist() == [120, 0] and set(el[:32].tolist()) == {0x7C} and set(el[32:].tolist()) == {0}
