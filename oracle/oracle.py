@@ -34,17 +34,29 @@ def _ptr(a, ty):
     return a.ctypes.data_as(ty)
 
 
+STAGED_TEXTS = ("test.py", "example_wrapper.py", "kernel_rope.cuh")
+
+
+def reference_tree():
+    """Where the reference's sources lie: SIDEAWARE_REFERENCE_TREE, else a checkout named
+    ``reference`` beside this repository; None when neither exists."""
+    cands = [os.environ.get("SIDEAWARE_REFERENCE_TREE"), os.path.join(_HERE, "..", "..", "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "example_llmc_rope.cu")):
+            return os.path.abspath(c)
+    return None
+
+
 def build(force: bool = False) -> None:
-    """Compile liboracle.so (and _ref/ when the reference tree is present)."""
+    """Compile liboracle.so and, where the reference tree is present, everything under _ref/:
+    the reference compiled in place and its harness texts staged unmodified."""
     if force or not os.path.exists(os.path.join(_HERE, "liboracle.so")) or (
         os.path.getmtime(os.path.join(_HERE, "liboracle.so")) < os.path.getmtime(os.path.join(_HERE, "rope_oracle.c"))
     ):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
-    ref_src = os.environ.get("SIDEAWARE_REFERENCE_TREE", "/root/reference")
-    if os.path.exists(os.path.join(ref_src, "example_llmc_rope.cu")) and (
-        force or not os.path.exists(os.path.join(_HERE, "_ref", "libref_rope.so"))
-        or not os.path.exists(os.path.join(_HERE, "_ref", "sideaware_reference.so"))
-    ):
+    ref_src = reference_tree()
+    wanted = ("libref_rope.so", "sideaware_reference.so") + STAGED_TEXTS
+    if ref_src and (force or not all(os.path.exists(os.path.join(_HERE, "_ref", f)) for f in wanted)):
         subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={ref_src}"], stdout=subprocess.DEVNULL)
 
 

@@ -1,7 +1,13 @@
 """Times an fp32 RoPE functor header through sideaware_create_kernel + sideaware_elementwise of the
 library given by path (this project's or the compiled reference: the header contract is the same),
 at the shape of the reference's own example (B=8 T=1024 32+32+32 heads HS=128, example_llmc_rope.cu:246-249),
-in place on a block from the library's allocator.  Checks the result against the oracle.  One JSON line."""
+in place on a block from the library's allocator.  Checks the result against the oracle.  One JSON line.
+
+    python rope_functor_timing_script.py <library> [include]
+
+With "include" the header registered is the literal text the reference's example registers,
+#include "kernel_rope.cuh" (example_llmc_rope.cu:135-144): NVRTC resolves it against the working
+directory, so the caller runs this script from the directory that holds the reference's header."""
 import ctypes
 import json
 import os
@@ -39,7 +45,9 @@ def main():
     tt = torch.from_numpy(table).cuda()
     buf = ctypes.c_void_p()
     assert lib.sideaware_malloc_async(ctypes.byref(buf), 4 * n, sp) == 0
-    kid = lib.sideaware_create_kernel(functors.rope_forward(T, NH, NH, HS, False).encode())
+    literal_include = len(sys.argv) > 2 and sys.argv[2] == "include"
+    header = b'#include "kernel_rope.cuh"' if literal_include else functors.rope_forward(T, NH, NH, HS, False).encode()
+    kid = lib.sideaware_create_kernel(header)
     assert kid >= 1
 
     def run():
@@ -53,6 +61,8 @@ def main():
     got = out.cpu().numpy()
     exact = got.tobytes() == want.tobytes()
     close = bool(np.allclose(got, want, rtol=1e-6, atol=1e-6))
+    # the reference's own criterion (validate_result, example_llmc_common.h:312-351, called with 1e-5)
+    ref_tol = bool((np.abs(got - want) <= 1e-5 + np.abs(want) * np.finfo(np.float32).eps).all())
     for _ in range(5):
         run()
     torch.cuda.synchronize()
@@ -65,7 +75,8 @@ def main():
     torch.cuda.synchronize()
     ms = statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(reps))
     moved = 2 * B * T * 2 * NH * HS * 4 + table.nbytes  # q and k read and written, table once
-    res = {"lib": path, "ms": ms, "gbs": moved / ms / 1e6, "bit_exact": exact, "within_1e-6": close}
+    res = {"lib": path, "ms": ms, "gbs": moved / ms / 1e6, "bit_exact": exact, "within_1e-6": close,
+           "within_reference_tolerance": ref_tol, "header": "literal include" if literal_include else "generated"}
     if hasattr(lib, "sideaware_rope_forward"):  # this project's ahead-of-time kernel on the same shape
         lib.sideaware_rope_forward.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 7 + [ctypes.c_void_p]
         aot = lambda: lib.sideaware_rope_forward(buf, tt.data_ptr(), B, T, NH, NH, HS, 0, 0, sp)  # noqa: E731

@@ -1,0 +1,96 @@
+"""The reference's own harness texts, UNMODIFIED, against this project's sideaware.so.
+
+oracle/Makefile stages test.py, example_wrapper.py and kernel_rope.cuh from the reference tree into
+oracle/_ref/ (never committed; it travels with the built libraries).  Where they are absent the tests
+skip.  Each runs in a process of its own because the reference's scripts install the pluggable
+allocator, which must happen before the first CUDA allocation of a process.
+
+ * test.py (test.py:163-326): metadata, torch.ops.sideaware.memcpy eagerly and under
+   torch.compile(fullgraph=True), the mixed-type functor through NVRTC, copies up to (200000, 20000) fp32;
+ * example_wrapper.py (example_wrapper.py:45-92): sideaware_init and the three custom ops;
+ * kernel_rope.cuh registered as the literal text #include "kernel_rope.cuh" (example_llmc_rope.cu:135-144),
+   compared with the oracle under the reference's tolerance (example_llmc_common.h:312-351).
+"""
+import json
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+STAGED = os.path.join(ROOT, "oracle", "_ref")
+OURS = os.path.join(ROOT, "l2_torch_alloc_b200", "sideaware.so")
+
+
+def staged(name):
+    return os.path.join(STAGED, name)
+
+
+def result_line(r):
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert r.returncode == 0 and lines, r.stdout[-3000:] + r.stderr[-3000:]
+    return json.loads(lines[-1][7:])
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(staged("test.py")), reason="the reference's test.py is not staged")
+def test_reference_test_py_runs_unmodified(tmp_path):
+    # test.py loads './sideaware.so' twice (test.py:14-16): give it a directory where that name is this library
+    os.symlink(OURS, tmp_path / "sideaware.so")
+    r = subprocess.run([sys.executable, staged("test.py")], capture_output=True, text=True, timeout=1500, cwd=tmp_path)
+    out = r.stdout
+    assert r.returncode == 0, out[-3000:] + r.stderr[-3000:]
+    assert "TESTING COMPLETE" in out
+    assert "Successfully compiled and executed the custom elementwise kernel" in out
+    assert "Incorrect output" not in out and "Skipped" not in out, out[-3000:]
+    verdicts = re.findall(r"Tensors equal: (\w+)", out)
+    assert len(verdicts) == 7 and all(v == "True" for v in verdicts), verdicts
+    # the two 8x8 copies: dst must show the source's values after the call
+    assert "After memcpy - src: 1.0 & 1.0, dst: 1.0 & 1.0" in out
+    assert "After compiled memcpy - src: 2.0 & 2.0, dst: 2.0 & 2.0" in out
+    m = re.search(r"SM sides metadata: \{'num_sms': (\d+), 'num_side0': (\d+), 'num_side1': (\d+), 'min_side': (\d+), 'hash': (\d+)\}", out)
+    assert m, out[:500]
+    n, s0, s1, mn, h = map(int, m.groups())
+    assert s0 + s1 == n and mn == min(s0, s1) and h & (1 << 21) and h & (1 << 12) and not h & 0xfff
+    print(r.stderr[-1500:])  # the library reports misuse and fallbacks on stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(staged("example_wrapper.py")), reason="the reference's example_wrapper.py is not staged")
+def test_reference_example_wrapper_runs_unmodified():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_wrapper_script.py"), STAGED, OURS],
+                       capture_output=True, text=True, timeout=900, cwd=ROOT)
+    res = result_line(r)
+    print(json.dumps(res))
+    assert "L2 Side Aware metadata" in r.stdout
+    assert res["enabled"] == 1 and res["side_index_consistent"] and res["side_counts_ok"]
+    assert res["memcpy_exact"] and res["one_to_one_exact"] and res["same_header_same_id"] and res["compiled_memcpy_exact"]
+    assert res["elementwise_max_bf16_ulp"] <= 1
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(staged("kernel_rope.cuh")), reason="the reference's kernel_rope.cuh is not staged")
+def test_reference_rope_header_included_literally():
+    # NVRTC resolves the quoted include against the working directory, as for the reference's example
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "rope_functor_timing_script.py"), OURS, "include"],
+                       capture_output=True, text=True, timeout=900, cwd=STAGED)
+    res = result_line(r)
+    print(json.dumps(res))
+    assert res["header"] == "literal include"
+    assert res["within_reference_tolerance"], "outside 1e-5 + |ref| * FLT_EPSILON"
+
+
+@pytest.mark.skipif(not os.path.exists(staged("kernel_rope.cuh")), reason="the reference's kernel_rope.cuh is not staged")
+def test_reference_rope_header_compiles_for_sm_100a_in_both_index_widths():
+    """No GPU needed: NVRTC compiles the staged header with the library's template, 32- and 64-bit size_type."""
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "import l2_torch_alloc_b200 as pkg\n"
+            "sa = pkg.SideAware()\n"
+            "for wide in (False, True):\n"
+            "    log = sa.compile_check(b'#include \"kernel_rope.cuh\"', wide)\n"
+            "    assert log == '', log\n"
+            "print('OK')\n") % ROOT
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=STAGED)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
