@@ -176,9 +176,11 @@ class SideAware:
         import torch
         tensors = [out0, out1, out2, out3, in0, in1, in2, in3]
         names = ["out0", "out1", "out2", "out3", "in0", "in1", "in2", "in3"]
-        # num_bytes is the byte size of the widest array, the one moved as 16-byte vectors
-        num_bytes = max((t.numel() * t.element_size() for t in tensors if t is not None), default=0)
-        assert num_bytes > 0
+        # num_bytes is the byte size of the one array the kernel moves as 16-byte vectors: in0, or out0 if its
+        # element is wider (sideaware.cu:127-129, :1378).  The other arrays may be any size the functor's
+        # index function asks for (a short broadcast table, a wider auxiliary array): they do not count.
+        num_bytes = max((t.numel() * t.element_size() for t in (in0, out0) if t is not None), default=0)
+        assert num_bytes > 0, "in0 or out0 must be given"
         ptrs = []
         for t, name in zip(tensors, names):
             assert t is None or (t.is_contiguous() and t.device.type == "cuda"), f"{name} must be contiguous"
@@ -238,6 +240,23 @@ class SideAware:
         assert out.numel() == a.numel() == b.numel()
         self.silu_mul_ptr(out.data_ptr(), a.data_ptr(), b.data_ptr(), float(scale), a.numel(), a.device.index,
                           torch.cuda.current_stream(a.device))
+
+    def mxfp8_quantize(self, out, scales, x) -> None:
+        """bf16 -> MXFP8 with functors.mxfp8_quantize_bf16: `out` uint8 (E4M3 bytes, one per element), `scales`
+        uint8 (E8M0 bytes, one per block of 32 elements; its size must be a multiple of 4), `x` bfloat16.
+        A block is reduced inside one warp instruction, which needs x to start on a 64-byte boundary; the
+        element count must be a multiple of 8 (whole 16-byte vectors), a last block of fewer than 32
+        elements is scaled by the elements it has."""
+        import torch
+        from . import functors
+        assert x.dtype == torch.bfloat16 and out.dtype == torch.uint8 and scales.dtype == torch.uint8
+        n = x.numel()
+        assert n % 8 == 0, "the element count must be a multiple of 8"
+        assert x.data_ptr() % 64 == 0, "x must start on a 64-byte boundary (a block of 32 elements may not straddle two warp instructions)"
+        assert out.numel() >= n and scales.numel() >= (n + 31) // 32 and scales.numel() % 4 == 0
+        assert n // 8 < 2 ** 31
+        kid = self.create_kernel(functors.mxfp8_quantize_bf16())
+        self.elementwise(kid, out[:n], None, None, None, x, None, None, None, scales.view(torch.int32), n // 8)
 
     def side_index_tensor(self):
         import torch

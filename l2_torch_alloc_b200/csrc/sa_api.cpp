@@ -182,7 +182,8 @@ SA_API void sideaware_elementwise(int kernel_id, size_t num_bytes,
         }
         if (sa_config().memcpy_engine.load() == 1) {
             if (!sa_prepare_launch(dev, stream, (uint64_t)in0, num_vecs, 0, forced_per_side, false, &s, &grid, &threads, sa_memcpy_bulk_warps())) return;
-            e = sa_launch_memcpy_bulk(s, dev->side_table, grid, out0, in0, (cudaStream_t)stream);
+            sa_report_wait_timeouts(dev, "sideaware_memcpy");
+            e = sa_launch_memcpy_bulk(s, dev->side_table, grid, out0, in0, sa_probe_wait_error_word(dev->probe), (cudaStream_t)stream);
             if (e != cudaSuccess) sa_set_error("sideaware_memcpy (bulk engine) launch: %s", cudaGetErrorString(e));
             return;
         }

@@ -301,12 +301,6 @@ bool sa_prepare_launch(SaDevice* dev, void* stream, uint64_t track_addr, uint64_
     std::memset(s, 0, sizeof(*s));
     int groups = parallel_groups > 0 ? parallel_groups : 4;
     if (groups > 4) groups = 4;
-    static const int forced_groups = [] { // tuning aid: SIDEAWARE_GROUPS = 256-thread groups per block
-        const char* e = std::getenv("SIDEAWARE_GROUPS");
-        int v = e ? std::atoi(e) : 0;
-        return (v >= 1 && v <= 4) ? v : 0;
-    }();
-    if (forced_groups && forced_groups < groups) groups = forced_groups; // may only lower a kernel's own choice
     int warps = exact_warps > 0 ? exact_warps : groups * 8;
     int g = dev->topo.num_sms;
     if (forced_per_side > 0 && 2 * forced_per_side < g) g = 2 * forced_per_side;
@@ -328,6 +322,14 @@ bool sa_prepare_launch(SaDevice* dev, void* stream, uint64_t track_addr, uint64_
     *threads = warps * 32;
     dev->launches.fetch_add(1);
     return true;
+}
+
+void sa_report_wait_timeouts(SaDevice* dev, const char* what) {
+    const unsigned long long now = sa_probe_wait_timeouts(dev->probe);
+    unsigned long long seen = dev->wait_timeouts_reported.load();
+    if (now > seen && dev->wait_timeouts_reported.compare_exchange_strong(seen, now))
+        sa_set_error("%s: %llu bounded waits ran out in bulk-copy kernels launched earlier on device %d; the chunks concerned "
+                     "were moved with ordinary loads and stores instead", what, now - seen, dev->id);
 }
 
 SaDevice* sa_device_if_ready(int device) {

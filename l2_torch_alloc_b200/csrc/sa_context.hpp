@@ -42,6 +42,7 @@ struct SaDevice {
     uint32_t full_hash = 0; // hash | 1 << 21 when usable, else 0
     SaSideTable side_table; // bit 0 of each byte = side of the SM; passed to every kernel
     std::atomic<unsigned long long> small_allocs{0}, launches{0}, jit_compiles{0};
+    std::atomic<unsigned long long> wait_timeouts_reported{0}; // of the device's wait-error word, how much has been reported
     SaJitDeviceCache* jit = nullptr;
     std::mutex jit_mu;
     ~SaDevice();
@@ -74,6 +75,10 @@ unsigned long long sa_error_total();
 bool sa_prepare_launch(SaDevice* dev, void* stream, uint64_t track_addr, uint64_t num_vecs, int parallel_groups,
                        int forced_per_side, bool reverse, SaSched* s, int* grid, int* threads,
                        int exact_warps = 0); // exact_warps > 0: that many warps per block, whatever the groups say
+
+// Records an error (once per new occurrence) if kernels launched earlier on this device counted waits that
+// ran out; called by the launchers of the kernels that have such waits.  Reads host memory only.
+void sa_report_wait_timeouts(SaDevice* dev, const char* what);
 
 // The device's state if some earlier call has already set it up, else nullptr.  Never
 // initialises anything (so it never allocates).

@@ -28,9 +28,9 @@ cudaError_t sa_launch_rope_table(float* table, const float* freqs, int half, int
 cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int device, int grid, int threads, void* dst, const void* src,
                                      cudaStream_t stream);
 // memcpy through bulk asynchronous copies staged in shared memory (sa_memcpy_bulk.cu); the block
-// size is fixed: sa_memcpy_bulk_warps() warps.
+// size is fixed: sa_memcpy_bulk_warps() warps.  `wait_errors`: device-visible word that counts waits that ran out.
 cudaError_t sa_launch_memcpy_bulk(const SaSched& s, const SaSideTable& sides, int grid, void* dst, const void* src,
-                                  cudaStream_t stream);
+                                  uint32_t* wait_errors, cudaStream_t stream);
 int sa_memcpy_bulk_warps();
 
 // Launch configuration shared by the ahead-of-time kernels.  Unless SIDEAWARE_PDL=0 the launch carries the

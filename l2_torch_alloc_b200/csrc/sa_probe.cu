@@ -121,6 +121,10 @@ struct SaProbeDevice {
     uint64_t* addrs = nullptr;    // [kMaxBatch]
     uint32_t* out_lat = nullptr;  // [kVotes][kMaxBatch]
     uint16_t* out_smid = nullptr; // [kVotes][kMaxBatch]
+    // one word of pinned host memory that kernels with bounded waits count into when a wait runs out
+    // (system-scope atomic): the host reads it without synchronising with the device
+    uint32_t* wait_errors_host = nullptr;
+    uint32_t* wait_errors_dev = nullptr;
     std::mutex mu;
     // ticket rings
     struct Ring { uint32_t* base = nullptr; unsigned next = 0; };
@@ -180,6 +184,10 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
     p->out_lat = (uint32_t*)c; c += up(sz_olat);
     p->out_smid = (uint16_t*)c; c += up(sz_osm);
 
+    if ((e = cudaHostAlloc((void**)&p->wait_errors_host, 64, cudaHostAllocMapped)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "cudaHostAlloc(wait-error word)"); }
+    *p->wait_errors_host = 0u;
+    if ((e = cudaHostGetDevicePointer((void**)&p->wait_errors_dev, p->wait_errors_host, 0)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "cudaHostGetDevicePointer"); }
+
     cudaDeviceProp prop;
     if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "cudaGetDeviceProperties"); }
     topo->device = device;
@@ -227,6 +235,7 @@ void sa_probe_destroy(SaProbeDevice* p) {
     if (!p) return;
     for (size_t i = 1; i < p->ring_blocks.size(); ++i) cudaFree(p->ring_blocks[i]);
     if (p->meta) cudaFree(p->meta);
+    if (p->wait_errors_host) cudaFreeHost(p->wait_errors_host);
     delete p;
 }
 
@@ -276,23 +285,10 @@ uint32_t* sa_probe_ticket_slot(SaProbeDevice* p, void* stream, bool* may_overlap
 }
 
 unsigned long long sa_probe_wait_timeouts(SaProbeDevice* p) {
-    std::vector<uint32_t*> blocks;
-    {
-        std::lock_guard<std::mutex> lock(p->ring_mu);
-        blocks = p->ring_blocks;
-    }
-    const int slots = kRingSlots * kRingsPerBlock;
-    std::vector<uint32_t> words(slots);
-    unsigned long long total = 0;
-    for (uint32_t* b : blocks) {
-        // word 96 of every slot: a strided copy of one uint32 per slot
-        if (cudaMemcpy2D(words.data(), sizeof(uint32_t), b + 96, sizeof(uint32_t) * kTicketStride, sizeof(uint32_t), slots,
-                         cudaMemcpyDeviceToHost) != cudaSuccess)
-            return total;
-        for (uint32_t w : words) total += w;
-    }
-    return total;
+    return p->wait_errors_host ? (unsigned long long)*(volatile uint32_t*)p->wait_errors_host : 0ull;
 }
+
+uint32_t* sa_probe_wait_error_word(SaProbeDevice* p) { return p->wait_errors_dev; }
 
 cudaError_t sa_probe_sides(SaProbeDevice* p, const SaTopology& topo, const uint64_t* addrs, int n,
                            uint8_t* sides_out, cudaStream_t stream, int* ambiguous_out) {

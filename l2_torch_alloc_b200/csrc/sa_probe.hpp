@@ -47,8 +47,11 @@ unsigned char* sa_probe_gpu_side_index(SaProbeDevice* p);
 // a ring could not be made.  *may_overlap_predecessor is false for the launches that have to wait for
 // the end of their predecessor on the stream, so that the ring is never overrun.
 uint32_t* sa_probe_ticket_slot(SaProbeDevice* p, void* stream, bool* may_overlap_predecessor);
-// Sum of the error words of all ticket slots (bounded waits in kernels that ran out); synchronous.
+// How many bounded waits inside kernels have run out so far on this device.  The kernels count into a
+// word of pinned host memory, so this neither synchronises nor copies.
 unsigned long long sa_probe_wait_timeouts(SaProbeDevice* p);
+// Device address of that word, a parameter of every kernel that waits on an mbarrier.
+uint32_t* sa_probe_wait_error_word(SaProbeDevice* p);
 
 // Pure host analysis of a latency matrix lat[sm][addr] (exposed for CPU tests).
 // offsets[j] is the byte offset of address j inside the probe page; offsets[0] == 0,

@@ -91,10 +91,17 @@ def mxfp8_quantize_bf16() -> str:
     """bf16 -> MXFP8 (OCP Microscaling Formats v1.0: blocks of 32 elements, elements FP8 E4M3, one shared
     power-of-two scale per block stored as E8M0), the use the reference names for custom vector functions
     (sideaware.cu:81-83).  out0 = the E4M3 bytes, the sideband array receives one scale byte per block
-    (pass it as a uint8 tensor viewed as int32).  A lane holds 8 elements, so the block maximum is taken
-    over the four lanes of a quad; the quad shuffles only if all four lanes are in this call together
-    (always, for an element count that is a multiple of 32 in a 64-byte-aligned array), otherwise each lane
-    scales by its own eight elements, so no lane can ever wait for one that does not come.
+    (pass it as a uint8 tensor viewed as int32), sideband_value = the number of 16-byte input vectors
+    (elements / 8; 0 = the element count is a multiple of 32).
+
+    A lane holds 8 elements, so a block is the four vectors of a lane quad and the block maximum is a
+    reduction over the quad.  Which lanes of a quad take part is worked out from the vector index and the
+    vector count, never from which lanes happen to be converged: in the last, partial block of an array
+    whose element count is not a multiple of 32 only the lanes that exist exchange values.  The input must
+    start on a 64-byte boundary (then vector 4k..4k+3 of the array are lanes 4j..4j+3 of one warp
+    instruction); SideAware.mxfp8_quantize checks that.  Only the exponent of the maximum matters, so it is
+    taken on the bf16 bit patterns (two elements per instruction), and the scaling is one exact
+    multiplication by a power of two.
     Scale: 2^(floor(log2(amax)) - 8), 8 being the largest E4M3 exponent; elements are rounded to nearest
     even and saturate at +-448.  A block of zeros gets the smallest scale (byte 0); bf16 subnormals count as zero
     (functor kernels are compiled with flush-to-zero)."""
@@ -110,26 +117,39 @@ constexpr bool input_evict[4] = {1, 0, 0, 0};
 #define CUSTOM_VECTOR_OP
 __device__ void vector_op(size_type vec_idx, int n, o0 *out0, o1 *out1, o2 *out2, o3 *out3,
                           const i0 *in0, const i1 *in1, const i2 *in2, const i3 *in3, int *mem, int val) {
-    float v[8];
-    float amax = 0.0f;
-    for (int e = 0; e < 8; e++) {
-        v[e] = e < n ? __bfloat162float(in0[e]) : 0.0f;
-        amax = fmaxf(amax, fabsf(v[e]));
+    const unsigned *w = (const unsigned *)in0; // 8 bf16 = 4 words
+    // magnitudes order like their 15-bit patterns: maximum of two elements per instruction
+    unsigned m = __vmaxu2(__vmaxu2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu),
+                          __vmaxu2(w[2] & 0x7fff7fffu, w[3] & 0x7fff7fffu));
+    m = max(m & 0xffffu, m >> 16);
+    const unsigned lane = threadIdx.x & 31u, first = lane & ~3u;
+    unsigned quad = 0xFu << first;
+    if (val > 0) { // vectors of this block that exist: all four except in the array's last block
+        const long long left = (long long)val - ((long long)vec_idx - (long long)(lane & 3u));
+        if (left < 4) quad = ((1u << (int)left) - 1u) << first;
     }
-    const unsigned lane = threadIdx.x & 31u;
-    const unsigned quad = 0xFu << (lane & ~3u);
-    if ((__activemask() & quad) == quad) {
-        amax = fmaxf(amax, __shfl_xor_sync(quad, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(quad, amax, 2));
+    if (quad == (0xFu << first)) {
+        m = max(m, __shfl_xor_sync(quad, m, 1));
+        m = max(m, __shfl_xor_sync(quad, m, 2));
+    } else {
+        for (unsigned i = 0; i < 4; i++)
+            if ((quad >> (first + i)) & 1u) m = max(m, __shfl_sync(quad, m, first + i));
     }
-    // floor(log2(amax)) is the exponent field of the float (bf16 values are never fp32 subnormals
-    // except bf16 subnormals, whose field is 0: they get the smallest scale, like zero)
-    int shared = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 8;
-    if (shared < -127) shared = -127;
-    // multiply by 2^-shared in two exact steps (2^127 and beyond are not floats)
-    const int h = (-shared) / 2, r = (-shared) - h;
-    const float s1 = __uint_as_float((unsigned)(127 + h) << 23), s2 = __uint_as_float((unsigned)(127 + r) << 23);
-    for (int e = 0; e < n; e++) out0[e] = __nv_fp8_e4m3(__fmul_rn(__fmul_rn(v[e], s1), s2));
-    if ((lane & 3u) == 0u) ((unsigned char*)mem)[vec_idx >> 2] = (unsigned char)(shared + 127);
+    // floor(log2(amax)) is the exponent field; bf16 subnormals have field 0 and get the smallest scale, like zero
+    const int field = (int)(m >> 7);
+    const int scale_byte = field > 8 ? field - 8 : 0;                   // E8M0: shared exponent + 127
+    const float mult = __uint_as_float((unsigned)(254 - scale_byte) << 23); // 2^-(shared exponent): 2^-120 .. 2^127
+    unsigned packed[2];
+    for (int i = 0; i < 2; i++) {
+        float2 a, b;
+        a.x = __fmul_rn(__uint_as_float(w[2 * i] << 16), mult);
+        a.y = __fmul_rn(__uint_as_float(w[2 * i] & 0xffff0000u), mult);
+        b.x = __fmul_rn(__uint_as_float(w[2 * i + 1] << 16), mult);
+        b.y = __fmul_rn(__uint_as_float(w[2 * i + 1] & 0xffff0000u), mult);
+        packed[i] = (unsigned)__nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3) |
+                    ((unsigned)__nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3) << 16);
+    }
+    *(uint2 *)out0 = make_uint2(packed[0], packed[1]);
+    if ((lane & 3u) == 0u) ((unsigned char *)mem)[vec_idx >> 2] = (unsigned char)scale_byte;
 }
 """

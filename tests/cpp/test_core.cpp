@@ -3,7 +3,8 @@
 //             for any side placement, hash, base address and array length
 //   alloc     allocator state machine on a simulated driver with fault injection
 //   topology  SM-side / hash discovery on synthetic latency matrices
-// Usage: test_core <sched|alloc|topology|all>
+//   ring      stage bookkeeping of the bulk-copy kernels, with loads that never arrive
+// Usage: test_core <sched|alloc|chunks|topology|ring|all>
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -15,6 +16,7 @@
 #include <vector>
 
 #include "../../l2_torch_alloc_b200/csrc/sa_alloc.hpp"
+#include "../../l2_torch_alloc_b200/csrc/sa_bulk.cuh"
 #include "../../l2_torch_alloc_b200/csrc/sa_probe.hpp"
 #include "../../l2_torch_alloc_b200/csrc/sa_sched.cuh"
 
@@ -778,6 +780,94 @@ static void test_topology() {
     std::printf("topology: done\n");
 }
 
+// ---------------------------------------------------------------------------
+// stage ring of the bulk-copy kernels (sa_bulk.cuh): replay what lane 0 of a warp does in
+// sa_memcpy_bulk_kernel against a model of the mbarriers, with chosen loads never arriving.
+// No GPU run can or should force a wait to run out, so the state after one is checked here.
+// ---------------------------------------------------------------------------
+struct ModelBarrier {
+    uint32_t completed = 0;   // phases completed so far
+    bool armed = false;       // a load is outstanding on the current phase
+    bool will_arrive = false; // ... and the model lets it arrive
+};
+
+static void ring_case(uint32_t S, uint32_t in_flight, uint32_t chunks, const std::set<uint32_t>& never_arrive) {
+    SaStageRing r;
+    sa_ring_reset(r);
+    std::vector<ModelBarrier> bar(S);
+    std::vector<uint32_t> chunk_of_stage(S, 0xffffffffu);
+    std::vector<int> stored(chunks, 0), plain(chunks, 0);
+    uint32_t rearmed_incomplete = 0, waits_after_failure_that_arrived = 0, errors = 0;
+    auto retire = [&]() {
+        const uint32_t st = sa_ring_oldest(r, S);
+        ModelBarrier& b = bar[st];
+        CHECK(b.armed);
+        // mbarrier.try_wait.parity succeeds when the phase with that parity has completed
+        const uint32_t parity = sa_ring_oldest_parity(r, S);
+        if (b.will_arrive) { b.completed++; b.armed = false; }
+        const bool arrived = !b.armed && ((b.completed - 1) & 1u) == parity;
+        if (arrived) {
+            stored[chunk_of_stage[st]]++;
+            if (r.failed) ++waits_after_failure_that_arrived;
+        } else {
+            ++errors;
+        }
+        sa_ring_retire(r, S, arrived);
+    };
+    for (uint32_t c = 0; c < chunks; ++c) {
+        if (sa_ring_may_issue(r)) {
+            const uint32_t st = sa_ring_issue(r, S);
+            if (bar[st].armed) ++rearmed_incomplete; // arming a barrier whose phase never completed
+            bar[st].armed = true;
+            bar[st].will_arrive = never_arrive.count(c) == 0;
+            chunk_of_stage[st] = c;
+            while (sa_ring_in_flight(r) > in_flight) retire();
+        } else {
+            plain[c]++; // the warp has given up on bulk copies
+        }
+    }
+    while (sa_ring_in_flight(r) > 0) retire();
+    for (uint32_t st = 0; st < S; ++st)
+        if ((r.lost >> st) & 1u) plain[chunk_of_stage[st]]++;
+    CHECK(rearmed_incomplete == 0);
+    CHECK(r.retired == r.issued);
+    CHECK((r.failed != 0) == (errors != 0));
+    bool once = true;
+    for (uint32_t c = 0; c < chunks; ++c) once = once && stored[c] + plain[c] == 1;
+    CHECK(once);
+    // nothing that never arrived was stored from shared memory
+    for (uint32_t c : never_arrive)
+        if (c < chunks) CHECK(stored[c] == 0);
+    if (never_arrive.empty()) {
+        CHECK(r.failed == 0 && r.lost == 0);
+        for (uint32_t c = 0; c < chunks; ++c) CHECK(stored[c] == 1);
+    } else if (*never_arrive.begin() < chunks) {
+        // the loads that were in flight behind the first lost one each got one more wait
+        const uint32_t first = *never_arrive.begin();
+        uint32_t expect_late = 0;
+        for (uint32_t c = first + 1; c < chunks && c <= first + in_flight; ++c) expect_late += never_arrive.count(c) == 0;
+        CHECK(waits_after_failure_that_arrived == expect_late);
+        // and nothing was issued after the failure was seen
+        CHECK(r.issued <= first + in_flight + 1);
+    }
+}
+
+static void test_ring() {
+    for (uint32_t S : {2u, 3u, 4u, 6u})
+        for (uint32_t L = 1; L + 1 < S || L == 1; ++L) {
+            if (L >= S) break;
+            for (uint32_t chunks : {0u, 1u, 2u, 5u, 64u, 1001u}) {
+                ring_case(S, L, chunks, {});
+                ring_case(S, L, chunks, {0});
+                ring_case(S, L, chunks, {3});
+                ring_case(S, L, chunks, {3, 4});
+                ring_case(S, L, chunks, {3, 5, 40});
+                ring_case(S, L, chunks, {chunks ? chunks - 1 : 0});
+            }
+        }
+    std::printf("ring: done\n");
+}
+
 int main(int argc, char** argv) {
     std::string what = argc > 1 ? argv[1] : "all";
     if (what == "sched" || what == "all") test_sched();
@@ -791,6 +881,7 @@ int main(int argc, char** argv) {
     }
     if (what == "chunks" || what == "all") test_alloc_chunks();
     if (what == "topology" || what == "all") test_topology();
+    if (what == "ring" || what == "all") test_ring();
     if (g_failures) {
         std::printf("%d CHECK(s) failed\n", g_failures);
         return 1;

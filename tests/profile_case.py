@@ -1,10 +1,11 @@
 """Small, self-terminating workloads for profiler captures.
 
-    python -m l2_torch_alloc_b200.profile_case memcpy   [--mib 256] [--reps 4] [--placement aware]
-    python -m l2_torch_alloc_b200.profile_case rope     [--batch 2]  [--reps 4]
-    python -m l2_torch_alloc_b200.profile_case functor  [--mib 256] [--reps 4]
-    python -m l2_torch_alloc_b200.profile_case functor-jit [--mib 256] [--reps 4]   (the same functor through NVRTC)
-    python -m l2_torch_alloc_b200.profile_case growth   [--mib 1024] [--reps 3]     (no kernel of interest: host time of
+    python -m tests.profile_case memcpy   [--mib 256] [--reps 4] [--placement aware]
+    python -m tests.profile_case rope     [--batch 2]  [--reps 4]
+    python -m tests.profile_case functor  [--mib 256] [--reps 4]
+    python -m tests.profile_case functor-jit [--mib 256] [--reps 4]   (the same functor through NVRTC)
+    python -m tests.profile_case mxfp8    [--mib 256] [--reps 3]      (bf16 -> MXFP8 functor; --mib is the input size)
+    python -m tests.profile_case growth   [--mib 1024] [--reps 3]     (no kernel of interest: host time of
                                                          first-touch allocation and the driver calls it took, as JSON)
 
 Each case touches more than the 126 MB L2 but well under 2 GB of device memory and
@@ -21,7 +22,7 @@ import l2_torch_alloc_b200 as pkg
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["memcpy", "rope", "functor", "functor-jit", "growth"])
+    ap.add_argument("case", choices=["memcpy", "rope", "functor", "functor-jit", "mxfp8", "growth"])
     ap.add_argument("--mib", type=int, default=256)
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--reps", type=int, default=4)
@@ -69,6 +70,17 @@ def main():
         sa.memcpy_ptr(out.data_ptr(), b, n)
         torch.cuda.synchronize()
         assert torch.equal(out, seed)
+    elif args.case == "mxfp8":
+        from l2_torch_alloc_b200 import functors
+        n = (args.mib << 20) // 2  # elements
+        x = torch.randn(n, device="cuda").to(torch.bfloat16)
+        a, o, sc = sa.malloc(2 * n), sa.malloc(max(n, 8 << 20)), sa.malloc(8 << 20)
+        sa.memcpy_ptr(a, x.data_ptr(), 2 * n)
+        kid = sa.create_kernel(functors.mxfp8_quantize_bf16())
+        sp = torch.cuda.current_stream().cuda_stream
+        for _ in range(args.reps):
+            sa.lib.sideaware_elementwise(kid, 2 * n, o, None, None, None, a, None, None, None, sc, n // 8, 0, 0, 0, sp)
+        torch.cuda.synchronize()
     elif args.case == "rope":
         B, T, Nq, Nkv, HS = args.batch, 8192, 32, 8, 128
         n = B * T * (Nq + 2 * Nkv) * HS

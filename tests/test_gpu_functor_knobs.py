@@ -164,8 +164,7 @@ def test_mxfp8_quantize_matches_restatement(sa):
     xin = torch.from_numpy(x_u16.view(np.int16)).cuda().view(torch.bfloat16)
     out = torch.zeros(n, dtype=torch.uint8, device="cuda")
     scales = torch.full(((blocks + 3) // 4 * 4,), 0xEE, dtype=torch.uint8, device="cuda")
-    kid = sa.create_kernel(functors.mxfp8_quantize_bf16())
-    sa.elementwise(kid, out, None, None, None, xin, None, None, None, scales.view(torch.int32), 0)
+    sa.mxfp8_quantize(out, scales, xin)
     torch.cuda.synchronize()
     got_el = out.cpu().numpy()
     got_sc = scales.cpu().numpy()
@@ -173,3 +172,73 @@ def test_mxfp8_quantize_matches_restatement(sa):
     assert (got_sc[blocks:] == 0xEE).all(), "no scale byte is written past the last block"
     bad = np.nonzero(got_el != want_el)[0]
     assert bad.size == 0, (bad[:10], got_el[bad[:10]], want_el[bad[:10]])
+
+
+@pytest.mark.parametrize("tail_vectors", [1, 2, 3])
+def test_mxfp8_last_partial_block_is_scaled_by_the_elements_it_has(sa, tail_vectors):
+    """Element counts that are not a multiple of 32: the last block has 8, 16 or 24 elements.  Its scale and its
+    elements must be those of a block padded with zeros (zeros cannot raise the maximum)."""
+    import torch
+    from oracle import oracle
+    blocks = 4099
+    n = blocks * 32 + tail_vectors * 8
+    rng = np.random.default_rng(0xB200 + 80 + tail_vectors)
+    x = rng.standard_normal(n).astype(np.float32) * np.exp2(rng.integers(-20, 20, size=n)).astype(np.float32)
+    x[-1] = 3.0e4  # the largest element of the partial block sits in its last vector
+    x_u16 = oracle.f32_to_bf16(x)
+    padded = np.concatenate([x_u16, np.zeros((blocks + 1) * 32 - n, dtype=np.uint16)])
+    want_el, want_sc = oracle.mxfp8_quantize_bf16(padded)
+    xin = torch.from_numpy(x_u16.view(np.int16)).cuda().view(torch.bfloat16)
+    out = torch.full((n + 64,), 0xEE, dtype=torch.uint8, device="cuda")
+    scales = torch.full(((blocks + 1 + 3) // 4 * 4 + 4,), 0xEE, dtype=torch.uint8, device="cuda")
+    sa.mxfp8_quantize(out, scales, xin)
+    torch.cuda.synchronize()
+    got_el, got_sc = out.cpu().numpy(), scales.cpu().numpy()
+    assert np.array_equal(got_sc[:blocks + 1], want_sc)
+    assert (got_sc[blocks + 1:] == 0xEE).all()
+    assert np.array_equal(got_el[:n], want_el[:n])
+    assert (got_el[n:] == 0xEE).all(), "nothing is written behind the last element"
+
+
+def test_mxfp8_helper_refuses_an_input_that_blocks_would_straddle(sa):
+    import torch
+    x = torch.zeros(4096 + 32, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    with pytest.raises(AssertionError, match="64-byte boundary"):
+        sa.mxfp8_quantize(out, scales, x[8:8 + 4096])  # 16 bytes in: legal for the kernel, wrong for the blocks
+    with pytest.raises(AssertionError, match="multiple of 8"):
+        sa.mxfp8_quantize(out, scales, x[:4092])
+
+
+WIDE_AUX = """
+#include <cuda_bf16.h>
+typedef __nv_bfloat16 o0;
+typedef __nv_bfloat16 i0;
+typedef float i1;
+struct unused {};
+typedef unused o1, o2, o3, i2, i3;
+constexpr bool reverse_order = false;
+constexpr bool input_evict[4] = {1, 1, 0, 0};
+__device__ void elementwise_op(size_t idx, int sideband, o0 &out0, o1 &out1, o2 &out2, o3 &out3,
+                               const i0 &in0, const i1 &in1, const i2 &in2, const i3 &in3) {
+    out0 = __float2bfloat16_rn(__bfloat162float(in0) + in1);
+}
+"""
+
+
+def test_auxiliary_array_wider_than_the_tracked_one_does_not_widen_the_launch(sa):
+    """in0 / out0 are bf16, in1 is fp32: in1 holds twice the bytes, but the number of 16-byte vectors follows
+    in0 (sideaware.cu:127-129).  Canary bytes behind out0 and in0 show that nothing ran past their end."""
+    import torch
+    n = 3 * (1 << 20) + 8 * 11
+    pad = 1 << 16
+    a_all = torch.full((n + pad,), 7.0, dtype=torch.bfloat16, device="cuda")
+    o_all = torch.full((n + pad,), -3.0, dtype=torch.bfloat16, device="cuda")
+    a_all[:n] = torch.randint(-64, 64, (n,), device="cuda").to(torch.bfloat16)
+    b = torch.randint(-64, 64, (n,), device="cuda").float()
+    kid = sa.create_kernel(WIDE_AUX)
+    sa.elementwise(kid, o_all[:n], None, None, None, a_all[:n], b, None, None)
+    torch.cuda.synchronize()
+    assert torch.equal(o_all[:n].float(), a_all[:n].float() + b)
+    assert bool((o_all[n:] == -3.0).all()) and bool((a_all[n:] == 7.0).all())
