@@ -153,6 +153,12 @@ int sideaware_get_placement(void);
  * shared memory, 4 KiB per copy; 0 = 128-bit vector loads/stores.  Same results. */
 void sideaware_set_memcpy_engine(int engine);
 int sideaware_get_memcpy_engine(void);
+/* The same choice for sideaware_rope_forward / _backward: 1 = the chunk is brought into
+ * shared memory by bulk copies, rotated there and sent back (V heads are never moved),
+ * 0 = 128-bit vector loads/stores from registers.  Bit-identical results.  Replaces the
+ * reference's JIT-ed kernel with kernel_rope.cuh:1-60 either way. */
+void sideaware_set_rope_engine(int engine);
+int sideaware_get_rope_engine(void);
 
 /* Per-chunk side map: writes one byte (0/1) per 4 KiB chunk of
  * [ptr, ptr + num_bytes) to host memory, as predicted from the address hash

@@ -68,6 +68,8 @@ SIGNATURES = {
     "sideaware_get_placement": (_i, []),
     "sideaware_set_memcpy_engine": (None, [_i]),
     "sideaware_get_memcpy_engine": (_i, []),
+    "sideaware_set_rope_engine": (None, [_i]),
+    "sideaware_get_rope_engine": (_i, []),
     "sideaware_chunk_sides": (_sz, [_vp, _sz, _vp]),
     "sideaware_verify_chunk_sides": (_i, [_vp, _sz, _i, c.c_uint]),
     "sideaware_get_stats": (None, [c.POINTER(Stats)]),

@@ -261,9 +261,16 @@ static sideaware_status_t rope_launch(void* qkv, const float* freqs_cis, int B, 
     const uint64_t num_vecs = (uint64_t)B * T * sh.vecs_per_row;
     SaSched s;
     int grid = 0, threads = 0;
-    // 768 threads per block: the rotation needs ~70 registers, measured faster than 1024 threads with spills
-    if (!sa_prepare_launch(dev, stream, (uint64_t)qkv, num_vecs, 3, 0, false, &s, &grid, &threads)) return cudaErrorMemoryAllocation;
-    cudaError_t e = sa_launch_rope(s, dev->side_table, grid, threads, qkv, freqs_cis, sh, dtype == 1, (cudaStream_t)stream);
+    cudaError_t e;
+    if (sa_config().rope_engine.load() == 1) {
+        if (!sa_prepare_launch(dev, stream, (uint64_t)qkv, num_vecs, 0, 0, false, &s, &grid, &threads, sa_rope_bulk_warps())) return cudaErrorMemoryAllocation;
+        sa_report_wait_timeouts(dev, "sideaware_rope_forward");
+        e = sa_launch_rope_bulk(s, dev->side_table, grid, qkv, freqs_cis, sh, dtype == 1, sa_probe_wait_error_word(dev->probe), (cudaStream_t)stream);
+    } else {
+        // 768 threads per block: the rotation needs ~70 registers, measured faster than 1024 threads with spills
+        if (!sa_prepare_launch(dev, stream, (uint64_t)qkv, num_vecs, 3, 0, false, &s, &grid, &threads)) return cudaErrorMemoryAllocation;
+        e = sa_launch_rope(s, dev->side_table, grid, threads, qkv, freqs_cis, sh, dtype == 1, (cudaStream_t)stream);
+    }
     if (e != cudaSuccess) sa_set_error("sideaware_rope_forward launch: %s", cudaGetErrorString(e));
     return e;
 }
@@ -388,6 +395,8 @@ SA_API void sideaware_set_placement(int mode) {
 SA_API int sideaware_get_placement(void) { return sa_config().placement.load(); }
 SA_API void sideaware_set_memcpy_engine(int engine) { sa_config().memcpy_engine.store(engine == 0 ? 0 : 1); }
 SA_API int sideaware_get_memcpy_engine(void) { return sa_config().memcpy_engine.load(); }
+SA_API void sideaware_set_rope_engine(int engine) { sa_config().rope_engine.store(engine == 0 ? 0 : 1); }
+SA_API int sideaware_get_rope_engine(void) { return sa_config().rope_engine.load(); }
 #endif
 
 // ---------------------------------------------------------------------------

@@ -243,7 +243,7 @@ bool init_device(SaDevice* dev) {
         std::string path = std::string(dump) + "." + std::to_string(dev->id) + ".json";
         if (FILE* f = std::fopen(path.c_str(), "w")) { std::fputs(dev->topo.json.c_str(), f); std::fclose(f); }
     }
-    dev->ready = true;
+    dev->ready.store(true, std::memory_order_release);
     return true;
 }
 
@@ -336,7 +336,7 @@ SaDevice* sa_device_if_ready(int device) {
     std::lock_guard<std::mutex> lock(g_devices_mu);
     if (device < 0 || device >= (int)g_devices.size() || !g_devices[device]) return nullptr;
     SaDevice* dev = g_devices[device].get();
-    return dev->ready ? dev : nullptr;
+    return dev->ready.load(std::memory_order_acquire) ? dev : nullptr;
 }
 
 void sa_backend_times(unsigned long long ns_out[8], unsigned long long calls_out[8]) {

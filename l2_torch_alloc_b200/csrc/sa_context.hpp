@@ -21,13 +21,15 @@ struct SaConfig {
     std::string log_file;          // JIT log destination ("" = none)
     std::atomic<int> placement{0};
     std::atomic<int> memcpy_engine{1}; // 0 = vector loads/stores, 1 = bulk copies through shared memory
+    std::atomic<int> rope_engine{0};   // the same choice for the RoPE kernels
 };
 SaConfig& sa_config();
 
 struct SaDevice {
     int id = -1;
     std::mutex mu;
-    bool ready = false, failed = false;
+    std::atomic<bool> ready{false}; // set last by the set-up, read without the lock by sa_device_if_ready
+    bool failed = false;
     std::string fail_why;
     const SaDriver* drv = nullptr;
     SaTopology topo;

@@ -19,13 +19,12 @@
 #include <mutex>
 
 #include "sa_kernels.hpp"
+#include "sa_rope_math.cuh"
 
 namespace {
 
 constexpr int kMaxThreads = 1024;
 
-// streaming (evict-first) 128-bit load: the data is used once
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 
 // ---------------------------------------------------------------------------
 // memcpy
@@ -40,7 +39,7 @@ sa_memcpy_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSi
             const uint4* p = src + e;
             uint4 r[SA_VEC_PER_LANE];
 #pragma unroll
-            for (int k = 0; k < SA_VEC_PER_LANE; ++k) r[k] = ld_stream(p + k * 32);
+            for (int k = 0; k < SA_VEC_PER_LANE; ++k) r[k] = sa_ld_stream(p + k * 32);
             uint4* q = dst + e;
 #pragma unroll
             for (int k = 0; k < SA_VEC_PER_LANE; ++k) q[k * 32] = r[k];
@@ -49,7 +48,7 @@ sa_memcpy_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSi
 #pragma unroll 1
             for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
                 uint64_t v = first_vec + k * 32 + lane;
-                if (v >= s.lead && v < s.end) dst[v - s.lead] = ld_stream(src + (v - s.lead));
+                if (v >= s.lead && v < s.end) dst[v - s.lead] = sa_ld_stream(src + (v - s.lead));
             }
         }
     });
@@ -58,78 +57,6 @@ sa_memcpy_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSi
 // ---------------------------------------------------------------------------
 // RoPE forward, in place on packed [B, T, Nq + 2 Nkv, HS]
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void rotate(float x, float y, float c, float s, float& ox, float& oy) {
-    // separate roundings, no fused multiply-add: identical to the host arithmetic of
-    // example_llmc_rope.cu:80-81 compiled without contraction
-    ox = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s));
-    oy = __fadd_rn(__fmul_rn(x, s), __fmul_rn(y, c));
-}
-
-// cos/sin entries that one 16-byte data vector needs: bf16 = 4 pairs (two float4), fp32 = 2 pairs (one)
-template <bool BF16>
-struct RopeTab {
-    float4 a, b;
-};
-
-// `inverse` flips the sign of the sine entries: x*c - y*(-s) = x*c + y*s and x*(-s) + y*c are,
-// bit for bit, what the reference's backward pass computes (example_llmc_rope.cu:191-192).
-template <bool BF16>
-__device__ __forceinline__ RopeTab<BF16> rope_load_tab(const float4* p, bool inverse) {
-    RopeTab<BF16> t;
-    t.a = __ldg(p);
-    if constexpr (BF16) t.b = __ldg(p + 1);
-    if (inverse) {
-        t.a.y = -t.a.y;
-        t.a.w = -t.a.w;
-        if constexpr (BF16) {
-            t.b.y = -t.b.y;
-            t.b.w = -t.b.w;
-        }
-    }
-    return t;
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint4 rope_apply(uint4 in, const RopeTab<BF16>& t) {
-    uint4 out;
-    if constexpr (BF16) {
-        auto pair = [](uint32_t w, float c, float s) {
-            float x = __uint_as_float(w << 16), y = __uint_as_float(w & 0xffff0000u);
-            float ox, oy;
-            rotate(x, y, c, s, ox, oy);
-            __nv_bfloat162 b = __floats2bfloat162_rn(ox, oy);
-            return *reinterpret_cast<uint32_t*>(&b);
-        };
-        out.x = pair(in.x, t.a.x, t.a.y);
-        out.y = pair(in.y, t.a.z, t.a.w);
-        out.z = pair(in.z, t.b.x, t.b.y);
-        out.w = pair(in.w, t.b.z, t.b.w);
-    } else {
-        float ox0, oy0, ox1, oy1;
-        rotate(__uint_as_float(in.x), __uint_as_float(in.y), t.a.x, t.a.y, ox0, oy0);
-        rotate(__uint_as_float(in.z), __uint_as_float(in.w), t.a.z, t.a.w, ox1, oy1);
-        out = make_uint4(__float_as_uint(ox0), __float_as_uint(oy0), __float_as_uint(ox1), __float_as_uint(oy1));
-    }
-    return out;
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint4 rope_vec(uint4 in, const float4* tab, bool inverse) {
-    return rope_apply<BF16>(in, rope_load_tab<BF16>(tab, inverse));
-}
-
-// Position of vector `e` (element index in 16-byte vectors): returns false for a V-head
-// vector, else the float4 index into the table.
-__device__ __forceinline__ bool rope_locate(const SaRopeShape& sh, uint64_t e, uint32_t* tab_idx) {
-    uint64_t row = e / sh.vecs_per_row;
-    uint32_t r = (uint32_t)(e - row * sh.vecs_per_row);
-    if (r >= sh.rotated_vecs) return false;
-    uint32_t tok = (uint32_t)(row % sh.T);
-    uint32_t pos = r % sh.vecs_per_head;
-    *tab_idx = tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec;
-    return true;
-}
-
 template <bool BF16, int THREADS>
 __global__ void __launch_bounds__(THREADS, 1)
 sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSideTable sides,
@@ -159,7 +86,7 @@ sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSide
             for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
                 uint32_t r, tok;
                 locate(k, r, tok);
-                if (r < sh.rotated_vecs) v[k] = ld_stream(p + k * 32);
+                if (r < sh.rotated_vecs) v[k] = sa_ld_stream(p + k * 32);
             }
             // When a head is a power-of-two number of vectors that divides the 32-lane stride, every
             // vector of this lane sits at the same place in its head: the cos/sin entries only change
@@ -188,7 +115,7 @@ sa_rope_kernel(const __grid_constant__ SaSched s, const __grid_constant__ SaSide
                 uint32_t ti;
                 if (a >= s.lead && a < s.end && rope_locate(sh, a - s.lead, &ti)) {
                     uint4* p = x + (a - s.lead);
-                    *p = rope_vec<BF16>(ld_stream(p), table + ti, sh.inverse != 0);
+                    *p = rope_vec<BF16>(sa_ld_stream(p), table + ti, sh.inverse != 0);
                 }
             }
         }
@@ -224,8 +151,8 @@ sa_silu_mul_kernel(const __grid_constant__ SaSched s, const __grid_constant__ Sa
                 uint4 ra[4], rb[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    ra[k] = ld_stream(a + e + (h * 4 + k) * 32);
-                    rb[k] = ld_stream(b + e + (h * 4 + k) * 32);
+                    ra[k] = sa_ld_stream(a + e + (h * 4 + k) * 32);
+                    rb[k] = sa_ld_stream(b + e + (h * 4 + k) * 32);
                 }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) out[e + (h * 4 + k) * 32] = silu_mul_vec(ra[k], rb[k], scale);
@@ -235,7 +162,7 @@ sa_silu_mul_kernel(const __grid_constant__ SaSched s, const __grid_constant__ Sa
             for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
                 uint64_t v = first_vec + k * 32 + lane;
                 if (v >= s.lead && v < s.end)
-                    out[v - s.lead] = silu_mul_vec(ld_stream(a + (v - s.lead)), ld_stream(b + (v - s.lead)), scale);
+                    out[v - s.lead] = silu_mul_vec(sa_ld_stream(a + (v - s.lead)), sa_ld_stream(b + (v - s.lead)), scale);
             }
         }
     });

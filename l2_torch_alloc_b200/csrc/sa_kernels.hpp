@@ -32,6 +32,10 @@ cudaError_t sa_launch_memcpy_noalloc(SaSched s, const SaSideTable& sides, int de
 cudaError_t sa_launch_memcpy_bulk(const SaSched& s, const SaSideTable& sides, int grid, void* dst, const void* src,
                                   uint32_t* wait_errors, cudaStream_t stream);
 int sa_memcpy_bulk_warps();
+// RoPE staged through shared memory with bulk copies (sa_rope_bulk.cu); fixed block size of sa_rope_bulk_warps() warps.
+cudaError_t sa_launch_rope_bulk(const SaSched& s, const SaSideTable& sides, int grid, void* x, const float* table,
+                                const SaRopeShape& sh, bool bf16, uint32_t* wait_errors, cudaStream_t stream);
+int sa_rope_bulk_warps();
 
 // Launch configuration shared by the ahead-of-time kernels.  Unless SIDEAWARE_PDL=0 the launch carries the
 // programmatic-stream-serialization attribute: when two of this library's kernels follow each other on a

@@ -185,6 +185,15 @@ def run_rope(sa, x_host, table, B, T, Nq, Nkv, HS, bf16, offset=0):
     return out
 
 
+@pytest.fixture(params=[0, 1], ids=["vector", "bulk"])
+def rope_engine(request, sa):
+    """Both RoPE engines (registers / staged through shared memory by bulk copies) must give the same bits."""
+    default = sa.lib.sideaware_get_rope_engine()
+    sa.lib.sideaware_set_rope_engine(request.param)
+    yield request.param
+    sa.lib.sideaware_set_rope_engine(default)
+
+
 ROPE_SHAPES = [  # B, T, Nq, Nkv, HS
     (4, 1024, 12, 12, 64),   # the CPU benchmark config of the reference function
     (2, 64, 32, 32, 128),    # the reference example's head geometry (example_llmc_rope.cu:246-249)
@@ -192,12 +201,14 @@ ROPE_SHAPES = [  # B, T, Nq, Nkv, HS
     (3, 33, 5, 2, 32),       # odd head counts, rows shorter than a 4 KiB chunk
     (1, 7, 1, 1, 8),         # tiny: several rows per chunk
     (2, 50, 6, 3, 48),       # head size that is not a power of two
+    (2, 40, 20, 6, 48),      # the same with rows longer than a chunk (the staged engine's two-run case)
+    (1, 300, 3, 1, 256),     # rows of exactly 5 KiB fp32 / 2.5 KiB bf16: run boundaries at odd places
 ]
 
 
 @pytest.mark.parametrize("shape", ROPE_SHAPES)
 @pytest.mark.parametrize("placement", ["aware", "wrong"])
-def test_rope_f32_bit_exact(sa, shape, placement):
+def test_rope_f32_bit_exact(sa, shape, placement, rope_engine):
     sa.set_placement(placement)
     B, T, Nq, Nkv, HS = shape
     rng = np.random.default_rng(0xB200 + 1)
@@ -211,7 +222,7 @@ def test_rope_f32_bit_exact(sa, shape, placement):
 
 
 @pytest.mark.parametrize("shape", ROPE_SHAPES)
-def test_rope_bf16_bit_exact(sa, shape):
+def test_rope_bf16_bit_exact(sa, shape, rope_engine):
     sa.set_placement("aware")
     B, T, Nq, Nkv, HS = shape
     rng = np.random.default_rng(0xB200 + 3)
@@ -224,18 +235,18 @@ def test_rope_bf16_bit_exact(sa, shape):
     assert np.array_equal(got[:, :, Nq + Nkv:], x[:, :, Nq + Nkv:]), "V heads must be untouched"
 
 
-def test_rope_unaligned_base(sa):
-    B, T, Nq, Nkv, HS = 2, 96, 8, 2, 64
-    rng = np.random.default_rng(3)
-    x = rng.uniform(-1, 1, size=(B, T, Nq + 2 * Nkv, HS)).astype(np.float32)
-    table = oracle.freqs_cis(HS, T, 10000.0, 0)
-    want = oracle.rope_forward_f32(x, table, B, T, Nq, Nkv, HS)
-    for off in (16, 4096 + 48, 8192 - 16):
-        got = run_rope(sa, x, table, B, T, Nq, Nkv, HS, bf16=False, offset=off)
-        assert got.tobytes() == want.tobytes()
+def test_rope_unaligned_base(sa, rope_engine):
+    for B, T, Nq, Nkv, HS in ((2, 96, 8, 2, 64), (2, 40, 16, 4, 128)):  # rows shorter and longer than a chunk
+        rng = np.random.default_rng(3)
+        x = rng.uniform(-1, 1, size=(B, T, Nq + 2 * Nkv, HS)).astype(np.float32)
+        table = oracle.freqs_cis(HS, T, 10000.0, 0)
+        want = oracle.rope_forward_f32(x, table, B, T, Nq, Nkv, HS)
+        for off in (16, 4096 + 48, 8192 - 16):
+            got = run_rope(sa, x, table, B, T, Nq, Nkv, HS, bf16=False, offset=off)
+            assert got.tobytes() == want.tobytes()
 
 
-def test_rope_matches_reference_golden_vectors(sa, golden_dir):
+def test_rope_matches_reference_golden_vectors(sa, golden_dir, rope_engine):
     g = np.load(os.path.join(golden_dir, "rope_small_f32.npz"))
     B, T, NH, HS = (int(v) for v in g["shape"])
     for scaled in (0, 1):
@@ -248,7 +259,7 @@ def test_rope_matches_reference_golden_vectors(sa, golden_dir):
 
 
 @pytest.mark.parametrize("shape", [(2, 64, 32, 32, 128), (2, 160, 32, 8, 128), (3, 33, 5, 2, 32), (2, 50, 6, 3, 48)])
-def test_rope_backward_matches_oracle(sa, shape, golden_dir):
+def test_rope_backward_matches_oracle(sa, shape, golden_dir, rope_engine):
     """In-place backward pass: equal to the oracle (example_llmc_rope.cu:166-195 restated); values compared
     as numbers because the reference adds into zeros, which turns -0 into +0."""
     B, T, Nq, Nkv, HS = shape
@@ -381,7 +392,7 @@ def test_rope_rejects_bad_shapes(sa):
     sa.free(buf)
 
 
-def test_rope_llama3_shape_properties(sa):
+def test_rope_llama3_shape_properties(sa, rope_engine):
     """Full benchmark shape B=8 T=8192 32q+8kv HS=128 bf16: one batch entry against the oracle,
     and every batch entry equal to it when all entries hold the same input (rotation depends on t, d only)."""
     import torch

@@ -10,6 +10,11 @@ error, and its second call leaves the amount of free device memory unchanged.
 The file is named to be collected last.  It passes on its own in a fresh process (the
 device has then not been set up by any allocating call, so the copy runs side-unaware)
 and after the other tests (the side table exists, so the copy runs side-aware)."""
+import json
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -80,3 +85,19 @@ def test_noalloc_rejects_what_it_cannot_do(sa):
     assert sa.lib.sideaware_memcpy_noalloc(t.data_ptr(), t.data_ptr(), 0, 0, None) == 0  # empty copy: nothing to do
     torch.cuda.synchronize()
     assert not t.any()
+
+
+def test_noalloc_as_the_first_call_of_a_process():
+    """In this test run the device has long been set up by earlier tests, so the branch the entry point exists
+    for (nothing allocated yet: symbol address looked up, no side table, side-unaware copy) is run in a
+    process of its own, where the allocation-free copy is the library's very first call."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    so = os.path.join(root, "l2_torch_alloc_b200", "sideaware.so")
+    r = subprocess.run([sys.executable, os.path.join(root, "tests", "noalloc_first_call_script.py"), so],
+                       capture_output=True, text=True, timeout=600, cwd=root)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert r.returncode == 0 and lines, r.stdout[-2000:] + r.stderr[-2000:]
+    res = json.loads(lines[-1][7:])
+    assert res["rcs"] == [0, 0] and res["equal"] == [True, True] and res["errors"] == 0, res
+    assert res["free_after_second"] == res["free_between"], "a call took device memory"
+    print("free device memory before the first call minus after it:", res["free_before_first"] - res["free_between"])
