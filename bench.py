@@ -43,9 +43,18 @@ ROPE_SHAPE = dict(B=8, T=8192, Nq=32, Nkv=8, HS=128)  # Llama-3-8B heads, bf16, 
 FUNCTOR_ELEMS = 1 << 30
 HBM_FALLBACK_GBS = 6650.0
 SPEC_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per 1 GiB launch of sa_memcpy_bulk_kernel, from the ncu
-# capture summarised in profiles/sa_memcpy_bulk_kernel_1GiB_fabric_by_placement.md
-MEMCPY_DRAM_TRAFFIC_BYTES = 2085908736
+WORKLOAD = "memcpy 1 GiB uint8 (seeded uniform random bytes)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one 1 GiB launch, per kernel, from an ncu capture of that
+# kernel at that size.  A profiler cannot run inside a timed benchmark, so this is NOT measured in the run:
+# the line says so (traffic_source) and carries null for a kernel that has no capture.
+PROFILED_DRAM_TRAFFIC_BYTES = {"sa_memcpy_bulk_kernel": 2085908736}
+
+
+def bench_config(n_gpus):
+    """The workload description; identical in both arms (how each arm runs it is in the line's `path`)."""
+    return {"workload": WORKLOAD, "bytes": MEMCPY_BYTES,
+            "l2": "inputs larger than L2 (2 GiB touched per step vs 126 MB)",
+            "parallelism": f"{n_gpus} independent replicas, no collective"}
 
 
 def env_int(name, default):
@@ -340,8 +349,7 @@ def run_reference(args, ranks):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": len(times), "warmup": warm, "ms_per_step": total / len(times) * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "memcpy 1 GiB uint8 (seeded uniform random bytes)", "bytes": MEMCPY_BYTES,
-                   "where": "host cores"},
+        "config": bench_config(args.gpus), "path": "libc memcpy on the host cores (rank 0 only)",
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{len(times)} x 1 GiB libc memcpy over {threads} threads "
                                    "(the reference ships no CPU memcpy; its check is dst == src)"},
@@ -470,78 +478,140 @@ def power_run(torch, fn, nbytes, seconds, index):
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
-def run_ours(args, ranks):
-    import numpy as np
-    import torch
+class Ctx:
+    """What the sections of the GPU arm share."""
 
-    import l2_torch_alloc_b200 as pkg
+    def __init__(self, args, ranks):
+        import torch
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    dev = ranks.local_rank % torch.cuda.device_count()
-    torch.cuda.set_device(dev)
-    sa = pkg.SideAware()  # raises if sideaware.so has not been built
-    lib = sa.lib
-    stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
-    summary = sa.summary_dict()
+        import l2_torch_alloc_b200 as pkg
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+        self.torch, self.args, self.ranks = torch, args, ranks
+        self.dev = ranks.local_rank % torch.cuda.device_count()
+        torch.cuda.set_device(self.dev)
+        torch.zeros(1, device="cuda")
+        torch.cuda.synchronize()
+        self.sa = pkg.SideAware()  # raises if sideaware.so has not been built
+        self.lib = self.sa.lib
+        t0 = time.perf_counter()
+        self.summary = self.sa.summary_dict()  # first use of the device: context check, probe page, discovery, side table
+        self.summary["init_ms"] = (time.perf_counter() - t0) * 1e3
+        self.stream = torch.cuda.current_stream()
+        self.sp = self.stream.cuda_stream
+        self.rt = load_cudart(torch)
+        self.peak, self.peak_kind = measured_peak()
 
-    def alloc(nbytes):
-        p = lib.sideaware_malloc_auto(nbytes, dev, sp)
+    def alloc(self, nbytes):
+        p = self.lib.sideaware_malloc_auto(nbytes, self.dev, self.sp)
         if not p:
-            raise MemoryError(sa.last_error())
+            raise MemoryError(self.sa.last_error())
         return p
 
-    # ---- headline: 1 GiB memcpy ------------------------------------------------
+    def free(self, p, nbytes):
+        self.lib.sideaware_free_auto(p, nbytes, self.dev, self.sp)
+
+    def kernel_entry(self, kernel, config, nbytes, fn, steps, warmup=3):
+        """One entry of roofline.kernels: `steps` launches back to back between two events (the way the headline is
+        timed: achieved = algorithmic bytes / average launch duration), plus a pass with an event after every launch."""
+        tot, _ = time_launches(self.torch, fn, steps, warmup, None, per_launch=False)
+        _, each = time_launches(self.torch, fn, steps, warmup, None, per_launch=True)
+        ms = tot / steps
+        return {"kernel": kernel, "config": config, "algorithmic_bytes": nbytes, "ms": ms, "achieved": gbs(nbytes, ms),
+                "frac": gbs(nbytes, ms) / self.peak, "launches": steps,
+                "event_per_launch_ms": statistics.mean(each), "event_per_launch_best_ms": min(each),
+                "event_per_launch_gbs": gbs(nbytes, statistics.mean(each))}
+
+
+def headline_memcpy(c):
+    """The timed region of the bench contract: K 1 GiB copies back to back, max over ranks."""
+    torch, lib, args, ranks = c.torch, c.lib, c.args, c.ranks
     gen = torch.Generator(device="cuda").manual_seed(0xB200 + 2 + ranks.rank)
-    seed_t = torch.randint(0, 256, (MEMCPY_BYTES,), dtype=torch.uint8, device="cuda", generator=gen)
-    src, dst = alloc(MEMCPY_BYTES), alloc(MEMCPY_BYTES)
-    lib.sideaware_memcpy(src, seed_t.data_ptr(), MEMCPY_BYTES, dev, sp)
+    c.seed_t = torch.randint(0, 256, (MEMCPY_BYTES,), dtype=torch.uint8, device="cuda", generator=gen)
+    c.src, c.dst = c.alloc(MEMCPY_BYTES), c.alloc(MEMCPY_BYTES)
+    lib.sideaware_memcpy(c.src, c.seed_t.data_ptr(), MEMCPY_BYTES, c.dev, c.sp)
     torch.cuda.synchronize()
-    launches_before = sa.stats()["kernel_launches"]
+    launches_before = c.sa.stats()["kernel_launches"]
 
     def step():
-        lib.sideaware_memcpy(dst, src, MEMCPY_BYTES, dev, sp)
+        lib.sideaware_memcpy(c.dst, c.src, MEMCPY_BYTES, c.dev, c.sp)
 
-    sa.set_placement("aware")
-    # the timed region: K launches back to back, one event before and one after (an event between two
-    # launches would keep consecutive kernels from overlapping launch and tail)
-    with ClockSampler(dev) as clocks:
+    c.step = step
+    c.sa.set_placement("aware")
+    # K launches back to back, one event before and one after (an event between two launches would keep
+    # consecutive kernels from overlapping launch and tail)
+    with ClockSampler(c.dev) as clocks:
         total_ms, _ = time_launches(torch, step, args.steps, args.warmup, ranks, per_launch=False)
-    launches = sa.stats()["kernel_launches"] - launches_before - args.warmup  # counted by the library itself
-    # a second, untimed-for-the-metric pass with an event after every launch, for best / median launch times
-    _, each = time_launches(torch, step, min(args.steps, 50), 3, None, per_launch=True)
+    launches = c.sa.stats()["kernel_launches"] - launches_before - args.warmup  # counted by the library itself
     worst_ms = ranks.max(total_ms)
     value = ranks.world * args.steps * 2 * MEMCPY_BYTES / (worst_ms * 1e-3) / 1e9
+    # the same launches for about a second, only to give the clock sampler more than a handful of samples
+    long_steps = max(args.steps, int(1000.0 / max(total_ms / args.steps, 1e-3)))
+    with ClockSampler(c.dev) as clocks_long:
+        time_launches(torch, step, long_steps, 0, None, per_launch=False)
+    _, each = time_launches(torch, step, min(args.steps, 50), 3, None, per_launch=True)
     # parity spot check of what was just timed
-    back = torch.empty_like(seed_t)
-    lib.sideaware_memcpy(back.data_ptr(), dst, MEMCPY_BYTES, dev, sp)
+    back = torch.empty_like(c.seed_t)
+    lib.sideaware_memcpy(back.data_ptr(), c.dst, MEMCPY_BYTES, c.dev, c.sp)
     torch.cuda.synchronize()
-    if not torch.equal(back, seed_t):
+    if not torch.equal(back, c.seed_t):
         raise SystemExit("bench: the timed copy is not bit-exact")
     del back
-
-    peak, peak_kind = measured_peak()
-    avg_launch_ms = total_ms / args.steps  # average launch duration over the timed region of this rank
+    avg_launch_ms = total_ms / args.steps
     achieved = gbs(2 * MEMCPY_BYTES, avg_launch_ms)
-    engine = lib.sideaware_get_memcpy_engine()
-    roofline = {"bound": "hbm", "kernel": "sa_memcpy_bulk_kernel" if engine == 1 else "sa_memcpy_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_spec_8000": achieved / SPEC_GBS,
-                "traffic": MEMCPY_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": 2 * MEMCPY_BYTES,
+    kernel = "sa_memcpy_bulk_kernel" if lib.sideaware_get_memcpy_engine() == 1 else "sa_memcpy_kernel"
+    traffic = PROFILED_DRAM_TRAFFIC_BYTES.get(kernel)
+    roofline = {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": c.peak, "unit": "GB/s",
+                "frac": achieved / c.peak, "peak_kind": f"of {c.peak_kind}", "frac_of_spec_8000": achieved / SPEC_GBS,
+                "traffic": traffic,
+                "traffic_source": ("ncu capture of one 1 GiB launch of this kernel (dram__bytes_read.sum + dram__bytes_write.sum); "
+                                   "not measured in this run") if traffic else None,
+                "algorithmic_bytes_per_launch": 2 * MEMCPY_BYTES,
                 "best_launch_ms": min(each), "median_launch_ms": statistics.median(each)}
+    entry = {"kernel": kernel, "config": "1 GiB uint8 copy, side-aware blocks", "algorithmic_bytes": 2 * MEMCPY_BYTES,
+             "ms": avg_launch_ms, "achieved": achieved, "frac": achieved / c.peak, "launches": args.steps,
+             "event_per_launch_ms": statistics.mean(each), "event_per_launch_best_ms": min(each),
+             "event_per_launch_gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(each))}
+    rep = clocks.report()
+    rep["one_second_of_the_same_launches"] = clocks_long.report()
+    return value, worst_ms, roofline, entry, rep, int(launches)
 
-    # ---- end to end through the C ABI with host buffers ---------------------------
-    e2e_steps = max(3, min(args.steps, 10))
+
+def pcie_limits(c):
+    """Pinned-memory copy rates of this box: each direction alone and both at once (what bounds any end-to-end figure)."""
+    torch, rt = c.torch, c.rt
+    n = 256 << 20
+    h_a = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    h_b = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    d_a = torch.empty(n, dtype=torch.uint8, device="cuda")
+    d_b = torch.empty(n, dtype=torch.uint8, device="cuda")
+    s2 = torch.cuda.Stream()
+    ms_up, _ = time_launches(torch, lambda: rt.cudaMemcpyAsync(d_a.data_ptr(), h_a.data_ptr(), n, 1, c.sp), 8, 2)
+    ms_dn, _ = time_launches(torch, lambda: rt.cudaMemcpyAsync(h_b.data_ptr(), d_b.data_ptr(), n, 2, c.sp), 8, 2)
+    ev0, ev1 = torch.cuda.Event(), torch.cuda.Event()
+
+    def both():
+        ev0.record(c.stream)
+        s2.wait_event(ev0)
+        rt.cudaMemcpyAsync(d_a.data_ptr(), h_a.data_ptr(), n, 1, c.sp)
+        rt.cudaMemcpyAsync(h_b.data_ptr(), d_b.data_ptr(), n, 2, s2.cuda_stream)
+        ev1.record(s2)
+        c.stream.wait_event(ev1)
+
+    ms_both, _ = time_launches(torch, both, 8, 2)
+    return {"h2d_gbs": gbs(n, ms_up / 8), "d2h_gbs": gbs(n, ms_dn / 8), "both_directions_each_gbs": gbs(n, ms_both / 8),
+            "note": "pinned host memory, 256 MiB copies; an end-to-end step moves its bytes once in each direction, so "
+                    "its GB/s (read + written bytes) cannot exceed twice the both-directions rate"}
+
+
+def e2e_memcpy(c):
+    """Host buffer -> device -> side-aware copy -> device -> host buffer, per step, pipelined over pieces on three streams."""
+    torch, lib, rt, ranks = c.torch, c.lib, c.rt, c.ranks
+    e2e_steps = max(3, min(c.args.steps, 10))
     h_src = torch.empty(MEMCPY_BYTES, dtype=torch.uint8, pin_memory=True)
     h_dst = torch.empty(MEMCPY_BYTES, dtype=torch.uint8, pin_memory=True)
-    h_src.copy_(seed_t)
+    h_src.copy_(c.seed_t)
     torch.cuda.synchronize()
-    rt = load_cudart(torch)
-
-    # One step moves the whole 1 GiB host buffer to the device, copies it there and brings the result
-    # back.  The three legs are pipelined over 64 MiB pieces on three streams (upload, kernel, download), so
-    # the two PCIe directions and the kernel overlap; every piece still goes host -> device -> kernel ->
-    # device -> host inside the timed region.
     piece = 64 << 20
     n_pieces = MEMCPY_BYTES // piece
     s_up, s_k, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
@@ -550,20 +620,20 @@ def run_ours(args, ranks):
     ev_begin, ev_done = torch.cuda.Event(), torch.cuda.Event()
 
     def e2e_step():
-        ev_begin.record(stream)
+        ev_begin.record(c.stream)
         for st_ in (s_up, s_k, s_down):
             st_.wait_event(ev_begin)
         for i in range(n_pieces):
             off = i * piece
-            rt.cudaMemcpyAsync(src + off, h_src.data_ptr() + off, piece, 1, s_up.cuda_stream)
+            rt.cudaMemcpyAsync(c.src + off, h_src.data_ptr() + off, piece, 1, s_up.cuda_stream)
             ev_up[i].record(s_up)
             s_k.wait_event(ev_up[i])
-            lib.sideaware_memcpy(dst + off, src + off, piece, dev, s_k.cuda_stream)
+            lib.sideaware_memcpy(c.dst + off, c.src + off, piece, c.dev, s_k.cuda_stream)
             ev_k[i].record(s_k)
             s_down.wait_event(ev_k[i])
-            rt.cudaMemcpyAsync(h_dst.data_ptr() + off, dst + off, piece, 2, s_down.cuda_stream)
+            rt.cudaMemcpyAsync(h_dst.data_ptr() + off, c.dst + off, piece, 2, s_down.cuda_stream)
         ev_done.record(s_down)
-        stream.wait_event(ev_done)
+        c.stream.wait_event(ev_done)
 
     e2e_ms, _ = time_launches(torch, e2e_step, e2e_steps, 2, ranks)
     e2e_worst = ranks.max(e2e_ms)
@@ -573,113 +643,209 @@ def run_ours(args, ranks):
     torch.cuda.synchronize()
     if not torch.equal(h_dst, h_src):
         raise SystemExit("bench: end-to-end copy mismatch")
-    e2e = {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": MEMCPY_BYTES, "d2h_bytes_per_step": MEMCPY_BYTES,
-           "steps": e2e_steps, "ms_per_step": e2e_worst / e2e_steps,
-           "pipeline": f"{n_pieces} pieces of {piece >> 20} MiB on 3 streams (upload / kernel / download overlap)"}
-    del h_src, h_dst
+    return {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": MEMCPY_BYTES, "d2h_bytes_per_step": MEMCPY_BYTES,
+            "steps": e2e_steps, "ms_per_step": e2e_worst / e2e_steps,
+            "pipeline": f"{n_pieces} pieces of {piece >> 20} MiB on 3 streams (upload / kernel / download overlap)"}
 
-    extra = {}
-    if ranks.rank == 0:
-        sub_steps = max(5, min(args.steps, 30))
-        # ---- the comparison set for the same 1 GiB copy -------------------------------
-        comp = {}
-        lib.sideaware_set_memcpy_engine(0)  # the 128-bit vector engine, for comparison with the default bulk engine
-        ms, ea = time_launches(torch, step, sub_steps, 3, None, per_launch=True)
-        comp["kernel_vector_engine_aware"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
-        lib.sideaware_set_memcpy_engine(1)
-        for mode in ("aware", "unaware", "wrong"):
-            sa.set_placement(mode)
-            ms, ea = time_launches(torch, step, sub_steps, 3, None, per_launch=True)
-            comp[f"kernel_{mode}"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
-        sa.set_placement("aware")
-        ms, ea = time_launches(torch, lambda: rt.cudaMemcpyAsync(dst, src, MEMCPY_BYTES, 3, sp), sub_steps, 3, None, per_launch=True)
-        comp["cudaMemcpyAsync_d2d"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
-        t_dst = torch.empty_like(seed_t)
-        ms, ea = time_launches(torch, lambda: t_dst.copy_(seed_t), sub_steps, 3, None, per_launch=True)
-        comp["torch_copy_"] = {"gbs": gbs(2 * MEMCPY_BYTES, statistics.mean(ea)), "best_gbs": gbs(2 * MEMCPY_BYTES, min(ea))}
-        del t_dst
-        extra["memcpy_comparison"] = comp
 
-        # ---- board power while copying (the reference's headline claim is power, sideaware.cu:4) ----
-        if ranks.world == 1 and args.power_seconds > 0:
-            power = {}
-            for mode in ("aware", "unaware"):
-                sa.set_placement(mode)
-                power[f"kernel_{mode}"] = power_run(torch, step, 2 * MEMCPY_BYTES, args.power_seconds, dev)
-            sa.set_placement("aware")
-            power["cudaMemcpyAsync_d2d"] = power_run(torch, lambda: rt.cudaMemcpyAsync(dst, src, MEMCPY_BYTES, 3, sp),
-                                                     2 * MEMCPY_BYTES, args.power_seconds, dev)
-            extra["power"] = power
-
-        # ---- size sweep 4 MiB .. 8 GiB (threshold lowered so 4 MiB blocks are side-aware too) ----
-        sweep = {}
-        lib.sideaware_alloc_threshold(4 << 20)
-        for shift in range(22, 34):
-            n = 1 << shift
-            try:
-                a, b = alloc(n), alloc(n)
-            except MemoryError:
-                break
-            f = lambda: lib.sideaware_memcpy(b, a, n, dev, sp)  # noqa: E731
-            reps = 40 if n <= (256 << 20) else 10
-            ms, ea = time_launches(torch, f, reps, 3, None, per_launch=True)
-            # back to back (no event between launches; events cost ~2 us each and are only 2 us fine)
-            tot, _ = time_launches(torch, f, reps, 3, None, per_launch=False)
-            g = lambda: rt.cudaMemcpyAsync(b, a, n, 3, sp)  # noqa: E731
-            tot_rt, _ = time_launches(torch, g, reps, 3, None, per_launch=False)
-            sweep[str(n)] = {"gbs": gbs(2 * n, statistics.median(ea)), "us": statistics.median(ea) * 1e3,
-                             "back_to_back_us": tot / reps * 1e3, "back_to_back_gbs": gbs(2 * n, tot / reps),
-                             "cudaMemcpyAsync_back_to_back_us": tot_rt / reps * 1e3,
-                             "cudaMemcpyAsync_back_to_back_gbs": gbs(2 * n, tot_rt / reps)}
-            lib.sideaware_free_auto(a, n, dev, sp)
-            lib.sideaware_free_auto(b, n, dev, sp)
-        lib.sideaware_alloc_threshold(8 << 20)
-        lib.sideaware_release_unused()
-        extra["memcpy_sweep"] = sweep
-
-    lib.sideaware_free_auto(src, MEMCPY_BYTES, dev, sp)
-    lib.sideaware_free_auto(dst, MEMCPY_BYTES, dev, sp)
-    del seed_t
+def flushed_launch_ms(c, fn, reps, flush_buf):
+    """Median duration of fn() when an L2-sized memset runs before every launch (the reference's timing method,
+    example_llmc_common.h:364-372): events bracket the launch only."""
+    torch = c.torch
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for _ in range(2):
+        fn()
+    for a, b in ev:
+        flush_buf.zero_()
+        a.record(c.stream)
+        fn()
+        b.record(c.stream)
     torch.cuda.synchronize()
+    return statistics.median(a.elapsed_time(b) for a, b in ev)
 
-    # ---- RoPE bf16 at the Llama-3-8B shape (every rank: its batch shard) ---------------------
+
+def run_script(script, *argv, timeout=900, cwd=None):
+    """Runs one of the committed timing scripts in a process of its own and returns its RESULT line."""
+    import subprocess
+    try:
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", script), *argv], capture_output=True, text=True,
+                           timeout=timeout, cwd=cwd or ROOT)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"{script} did not finish in {timeout} s"}
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("RESULT ")]
+    if r.returncode != 0 or not lines:
+        return {"unavailable": (r.stderr or r.stdout)[-300:]}
+    return json.loads(lines[-1][7:])
+
+
+def comparison_memcpy(c):
+    """The same 1 GiB copy by: both engines, the three placements, cudaMemcpyAsync, torch copy_, and the reference's
+    own library (its allocator and its JIT-ed kernel, compiled from the reference's sources) in a process of its own."""
+    torch, lib, rt, sa = c.torch, c.lib, c.rt, c.sa
+    sub_steps = max(5, min(c.args.steps, 30))
+    nb = 2 * MEMCPY_BYTES
+
+    def measure(fn):
+        _, ea = time_launches(torch, fn, sub_steps, 3, None, per_launch=True)
+        tot, _ = time_launches(torch, fn, sub_steps, 3, None, per_launch=False)
+        return {"gbs": gbs(nb, statistics.mean(ea)), "best_gbs": gbs(nb, min(ea)), "back_to_back_gbs": gbs(nb, tot / sub_steps)}
+
+    comp = {}
+    lib.sideaware_set_memcpy_engine(0)  # the 128-bit vector engine, for comparison with the default bulk engine
+    comp["kernel_vector_engine_aware"] = measure(c.step)
+    lib.sideaware_set_memcpy_engine(1)
+    for mode in ("aware", "unaware", "wrong"):
+        sa.set_placement(mode)
+        comp[f"kernel_{mode}"] = measure(c.step)
+    sa.set_placement("aware")
+    comp["cudaMemcpyAsync_d2d"] = measure(lambda: rt.cudaMemcpyAsync(c.dst, c.src, MEMCPY_BYTES, 3, c.sp))
+    t_dst = torch.empty_like(c.seed_t)
+    comp["torch_copy_"] = measure(lambda: t_dst.copy_(c.seed_t))
+    del t_dst
+    return comp
+
+
+def reference_gpu_library(c):
+    """The reference's own GPU path on this box, where oracle/_ref holds it: memcpy at 1 GiB, its RoPE header through
+    its NVRTC template at the reference example's shape, and llm.c's naive RoPE kernel at the same shape.  Each runs
+    in a process of its own, outside every timed region of this file (the two libraries export the same symbols)."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    ref_so = os.path.join(ref_dir, "sideaware_reference.so")
+    ours_so = os.path.join(ROOT, "l2_torch_alloc_b200", "sideaware.so")
+    if not os.path.exists(ref_so):
+        return None, None
+    mem, rope = {}, {}
+    one_gib = str(1 << 30)
+    for name, so in (("reference_library", ref_so), ("this_library_same_script", ours_so)):
+        r = run_script("memcpy_timing_script.py", so, one_gib)
+        mem[name] = r["sizes"][one_gib] if "sizes" in r else r
+    for name, so in (("reference_library_nvrtc", ref_so), ("this_library_nvrtc", ours_so)):
+        rope[name] = run_script("rope_functor_timing_script.py", so)
+    if os.path.exists(os.path.join(ref_dir, "kernel_rope.cuh")):
+        rope["this_library_nvrtc_reference_header_included"] = run_script("rope_functor_timing_script.py", ours_so, "include", cwd=ref_dir)
+        rope["reference_library_nvrtc_reference_header_included"] = run_script("rope_functor_timing_script.py", ref_so, "include", cwd=ref_dir)
+    rope["llmc_naive_kernel1"] = run_script("naive_rope_timing_script.py")
+    rope["config"] = "fp32 B=8 T=1024 32+32+32 heads HS=128 in place (the reference example's shape)"
+    return mem, rope
+
+
+def power_section(c):
+    """Board power while copying (the reference's headline claim is power, sideaware.cu:4)."""
+    power = {}
+    for mode in ("aware", "unaware"):
+        c.sa.set_placement(mode)
+        power[f"kernel_{mode}"] = power_run(c.torch, c.step, 2 * MEMCPY_BYTES, c.args.power_seconds, c.dev)
+    c.sa.set_placement("aware")
+    power["cudaMemcpyAsync_d2d"] = power_run(c.torch, lambda: c.rt.cudaMemcpyAsync(c.dst, c.src, MEMCPY_BYTES, 3, c.sp),
+                                             2 * MEMCPY_BYTES, c.args.power_seconds, c.dev)
+    return power
+
+
+def sweep_memcpy(c):
+    """4 MiB .. 8 GiB (threshold lowered so 4 MiB blocks are side-aware too).  Sizes whose source and destination fit
+    the 126 MB L2 together are L2 figures when launched back to back, so every size up to 256 MiB is also timed with an
+    L2-sized memset before each launch."""
+    torch, lib, rt = c.torch, c.lib, c.rt
+    sweep = {}
+    flush_buf = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
+    lib.sideaware_alloc_threshold(4 << 20)
+    for shift in range(22, 34):
+        n = 1 << shift
+        try:
+            a, b = c.alloc(n), c.alloc(n)
+        except MemoryError:
+            break
+        f = lambda: lib.sideaware_memcpy(b, a, n, c.dev, c.sp)  # noqa: E731
+        g = lambda: rt.cudaMemcpyAsync(b, a, n, 3, c.sp)  # noqa: E731
+        reps = 40 if n <= (256 << 20) else 10
+        _, ea = time_launches(torch, f, reps, 3, None, per_launch=True)
+        tot, _ = time_launches(torch, f, reps, 3, None, per_launch=False)
+        tot_rt, _ = time_launches(torch, g, reps, 3, None, per_launch=False)
+        row = {"gbs": gbs(2 * n, statistics.median(ea)), "us": statistics.median(ea) * 1e3,
+               "back_to_back_us": tot / reps * 1e3, "back_to_back_gbs": gbs(2 * n, tot / reps),
+               "cudaMemcpyAsync_back_to_back_us": tot_rt / reps * 1e3,
+               "cudaMemcpyAsync_back_to_back_gbs": gbs(2 * n, tot_rt / reps),
+               "back_to_back_is": "L2-resident" if 2 * n <= (126 << 20) else "larger than L2"}
+        if n <= (256 << 20):
+            ms_f = flushed_launch_ms(c, f, 20, flush_buf)
+            ms_g = flushed_launch_ms(c, g, 20, flush_buf)
+            row.update({"l2_flushed_us": ms_f * 1e3, "l2_flushed_gbs": gbs(2 * n, ms_f),
+                        "cudaMemcpyAsync_l2_flushed_us": ms_g * 1e3, "cudaMemcpyAsync_l2_flushed_gbs": gbs(2 * n, ms_g)})
+        sweep[str(n)] = row
+        c.free(a, n)
+        c.free(b, n)
+    lib.sideaware_alloc_threshold(8 << 20)
+    lib.sideaware_release_unused()
+    del flush_buf
+    return sweep
+
+
+def rope_section(c):
+    """RoPE bf16 at the Llama-3-8B shape; every rank runs it on its own batch shard."""
+    torch, lib, sa, ranks = c.torch, c.lib, c.sa, c.ranks
     S = ROPE_SHAPE
     H = S["Nq"] + 2 * S["Nkv"]
     rope_elems = S["B"] * S["T"] * H * S["HS"]
-    rope_bytes_moved = 2 * S["B"] * S["T"] * (S["Nq"] + S["Nkv"]) * S["HS"] * 2 + S["T"] * S["HS"] * 4
+    moved = 2 * S["B"] * S["T"] * (S["Nq"] + S["Nkv"]) * S["HS"] * 2 + S["T"] * S["HS"] * 4
     gen = torch.Generator(device="cuda").manual_seed(0xB200 + 3 + ranks.rank)
     x = torch.randn(rope_elems, dtype=torch.float32, device="cuda", generator=gen).to(torch.bfloat16)
-    qkv = alloc(rope_elems * 2)
-    lib.sideaware_memcpy(qkv, x.data_ptr(), rope_elems * 2, dev, sp)
+    qkv = c.alloc(rope_elems * 2)
+    lib.sideaware_memcpy(qkv, x.data_ptr(), rope_elems * 2, c.dev, c.sp)
     half = S["HS"] // 2
     inv = 1.0 / (500000.0 ** (torch.arange(0, half, dtype=torch.float32) * 2 / S["HS"]))
     ang = torch.arange(S["T"], dtype=torch.float32)[:, None] * inv[None, :]
     table = torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous().cuda()
+    cfg = "bf16 B=8 T=8192 32q+8kv HS=128 theta=500000 in place"
 
     def rope_step():
-        rc = lib.sideaware_rope_forward(qkv, table.data_ptr(), S["B"], S["T"], S["Nq"], S["Nkv"], S["HS"], 1, dev, sp)
+        rc = lib.sideaware_rope_forward(qkv, table.data_ptr(), S["B"], S["T"], S["Nq"], S["Nkv"], S["HS"], 1, c.dev, c.sp)
         if rc:
             raise SystemExit(f"rope launch failed: {sa.last_error()}")
 
-    rope_steps = max(5, min(args.steps, 50))
-    rope = {}
-    for mode in (("aware", "unaware", "wrong") if ranks.rank == 0 else ("aware",)):
-        sa.set_placement(mode)
-        ms, ea = time_launches(torch, rope_step, rope_steps, 3, ranks if mode == "aware" else None, per_launch=True)
-        if mode == "aware":
-            worst = ranks.max(ms)
-            rope["aggregate_gbs"] = ranks.world * rope_steps * rope_bytes_moved / (worst * 1e-3) / 1e9
-        rope[mode] = {"gbs": gbs(rope_bytes_moved, statistics.mean(ea)), "best_gbs": gbs(rope_bytes_moved, min(ea)),
-                      "ms": statistics.mean(ea)}
-    sa.set_placement("aware")
-    if ranks.rank == 0:  # the same launches with no event between them, as the headline is timed
-        tot, _ = time_launches(torch, rope_step, rope_steps, 3, None, per_launch=False)
-        rope["aware"]["back_to_back_gbs"] = gbs(rope_bytes_moved, tot / rope_steps)
-    rope["algorithmic_bytes"] = rope_bytes_moved
-    rope["frac_of_peak"] = rope["aware"]["gbs"] / peak
-    rope["config"] = "bf16 B=8 T=8192 32q+8kv HS=128 theta=500000 in place"
-    lib.sideaware_free_auto(qkv, rope_elems * 2, dev, sp)
+    steps = max(5, min(c.args.steps, 50))
+    rope = {"algorithmic_bytes": moved, "config": cfg}
+    # the job-wide figure: all ranks together, slowest rank's time, launches back to back as for the headline
+    tot, _ = time_launches(torch, rope_step, steps, 3, ranks, per_launch=False)
+    rope["aggregate_gbs"] = ranks.world * steps * moved / (ranks.max(tot) * 1e-3) / 1e9
+    entries = []
+    default_engine = lib.sideaware_get_rope_engine()
+    kernel_names = {0: "sa_rope_kernel<bf16>", 1: "sa_rope_bulk_kernel<bf16>"}
+    entries.append(c.kernel_entry(kernel_names[default_engine], cfg, moved, rope_step, steps))
+    rope["aware"] = {"gbs": entries[0]["event_per_launch_gbs"], "best_gbs": gbs(moved, entries[0]["event_per_launch_best_ms"]),
+                     "back_to_back_gbs": entries[0]["achieved"], "ms": entries[0]["event_per_launch_ms"]}
+    rope["frac_of_peak"] = entries[0]["frac"]
     if ranks.rank == 0:
+        for mode in ("unaware", "wrong"):
+            sa.set_placement(mode)
+            _, ea = time_launches(torch, rope_step, steps, 3, None, per_launch=True)
+            tot, _ = time_launches(torch, rope_step, steps, 3, None, per_launch=False)
+            rope[mode] = {"gbs": gbs(moved, statistics.mean(ea)), "best_gbs": gbs(moved, min(ea)),
+                          "back_to_back_gbs": gbs(moved, tot / steps), "ms": statistics.mean(ea)}
+        sa.set_placement("aware")
+        other = 1 - default_engine
+        lib.sideaware_set_rope_engine(other)
+        e = c.kernel_entry(kernel_names[other], cfg + " (the engine that is not the default)", moved, rope_step, steps)
+        lib.sideaware_set_rope_engine(default_engine)
+        rope["other_engine"] = e
+
+        # end to end for RoPE: pinned host tensor -> device -> rotation in place -> pinned host, per step
+        if ranks.world == 1:
+            nbytes = rope_elems * 2
+            h = torch.empty(rope_elems, dtype=torch.bfloat16, pin_memory=True)
+            h.copy_(x)
+            torch.cuda.synchronize()
+
+            def e2e_rope_step():
+                c.rt.cudaMemcpyAsync(qkv, h.data_ptr(), nbytes, 1, c.sp)
+                rope_step()
+                c.rt.cudaMemcpyAsync(h.data_ptr(), qkv, nbytes, 2, c.sp)
+
+            ms, _ = time_launches(torch, e2e_rope_step, 3, 1, None)
+            rope["e2e"] = {"value": gbs(moved, ms / 3), "unit": "GB/s (same algorithmic bytes as the kernel figure)",
+                           "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": ms / 3,
+                           "note": "whole tensor up, one launch, whole tensor down on one stream"}
+            del h
+
         # torch eager on the same packed tensor (fp32 math on the q,k heads, written back as bf16), as a baseline
         xt = x.view(S["B"], S["T"], H, S["HS"])
         rot = S["Nq"] + S["Nkv"]
@@ -692,100 +858,164 @@ def run_ours(args, ranks):
             im = qk[..., 0] * sin + qk[..., 1] * cos
             xt[:, :, :rot, :] = torch.stack((re, im), dim=-1).view(S["B"], S["T"], rot, S["HS"]).to(torch.bfloat16)
 
-        ms, ea = time_launches(torch, eager_rope, 5, 2, None, per_launch=True)
-        rope["torch_eager"] = {"gbs": gbs(rope_bytes_moved, statistics.mean(ea)), "ms": statistics.mean(ea)}
-        if ranks.world == 1 and not args.no_torch_compile:
-            rope["torch_compile"] = compiled_baseline(torch, eager_rope, rope_bytes_moved)
+        _, ea = time_launches(torch, eager_rope, 5, 2, None, per_launch=True)
+        rope["torch_eager"] = {"gbs": gbs(moved, statistics.mean(ea)), "ms": statistics.mean(ea)}
+        if ranks.world == 1 and not c.args.no_torch_compile:
+            rope["torch_compile"] = compiled_baseline(torch, eager_rope, moved)
         del xt, cos, sin
+    c.free(qkv, rope_elems * 2)
     del x, table
+    return rope, entries
 
-    # ---- functor: out = bf16(a * sigmoid(a) * b * 0.5), 2^30 elements (rank 0) ----------------
-    functor = None
-    if ranks.rank == 0:
-        from l2_torch_alloc_b200 import functors
-        n = FUNCTOR_ELEMS
-        a, b, o = alloc(2 * n), alloc(2 * n), alloc(2 * n)
-        g2 = torch.Generator(device="cuda").manual_seed(0xB200 + 4)
-        chunk = 1 << 27
-        for off in range(0, n, chunk):
-            for buf in (a, b):
-                t = torch.randn(chunk, dtype=torch.float32, device="cuda", generator=g2).to(torch.bfloat16)
-                lib.sideaware_memcpy(buf + 2 * off, t.data_ptr(), 2 * chunk, dev, sp)
-        torch.cuda.synchronize()
-        kid = sa.create_kernel(functors.silu_mul_bf16())
-        scale_bits = int(np.float32(0.5).view(np.int32))
-        f_jit = lambda: lib.sideaware_elementwise(kid, 2 * n, o, None, None, None, a, b, None, None, None, scale_bits, 0, 0, dev, sp)  # noqa: E731
-        f_aot = lambda: lib.sideaware_silu_mul_bf16(o, a, b, 0.5, n, dev, sp)  # noqa: E731
-        functor = {"algorithmic_bytes": 6 * n, "config": "bf16 2^30 elements, three side-tagged buffers"}
-        for name, f in (("aot", f_aot), ("nvrtc", f_jit)):
-            for mode in ("aware", "unaware"):
-                sa.set_placement(mode)
-                ms, ea = time_launches(torch, f, 10, 2, None, per_launch=True)
-                functor[f"{name}_{mode}"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea)}
-        sa.set_placement("aware")
-        for name, f in (("aot", f_aot), ("nvrtc", f_jit)):
-            tot, _ = time_launches(torch, f, 10, 2, None, per_launch=False)
-            functor[f"{name}_aware"]["back_to_back_gbs"] = gbs(6 * n, tot / 10)
-        functor["frac_of_peak"] = functor["aot_aware"]["gbs"] / peak
-        for buf in (a, b, o):
-            lib.sideaware_free_auto(buf, 2 * n, dev, sp)
-        # torch eager F.silu(a) * b * 0.5 on torch-allocated tensors of the same size, as a baseline
-        ta = torch.randn(n, dtype=torch.float32, device="cuda", generator=g2).to(torch.bfloat16) if n <= (1 << 28) else None
-        if ta is None:
-            ta = torch.empty(n, dtype=torch.bfloat16, device="cuda").normal_(generator=g2)
-        tb = torch.empty(n, dtype=torch.bfloat16, device="cuda").normal_(generator=g2)
-        ms, ea = time_launches(torch, lambda: torch.nn.functional.silu(ta) * tb * 0.5, 5, 2, None, per_launch=True)
-        functor["torch_eager"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea),
-                                  "note": "three kernels with bf16 temporaries; GB/s counts the same 6 bytes per element"}
-        if ranks.world == 1 and not args.no_torch_compile:
-            functor["torch_compile"] = compiled_baseline(torch, lambda: torch.nn.functional.silu(ta) * tb * 0.5, 6 * n)
-        del ta, tb
-        if sa.error_count():
-            functor["errors"] = sa.last_error()
 
-    churn = None
-    if ranks.rank == 0 and ranks.world == 1 and args.churn_ops > 0:
-        lib.sideaware_release_unused()
-        torch.cuda.synchronize()
-        churn = {"sideaware": allocator_churn(lib, rt, dev, sp, args.churn_ops)}
-        churn["sideaware"]["stats"] = sa.stats()
-        # the same sequence again with what the first pass mapped still mapped: the steady state of a program
-        # whose sizes repeat (no driver calls at all if every request finds a free run)
-        before_warm = sa.stats()
-        churn["sideaware_second_pass"] = allocator_churn(lib, rt, dev, sp, args.churn_ops)
-        after_warm = sa.stats()
-        churn["sideaware_second_pass"]["handles_created"] = after_warm["handles_created"] - before_warm["handles_created"]
-        churn["sideaware_second_pass"]["served_from_mapped_runs"] = after_warm["reuse_hits"] - before_warm["reuse_hits"]
-        churn["sideaware_second_pass"]["large_allocs"] = after_warm["large_allocs"] - before_warm["large_allocs"]
-        lib.sideaware_release_unused()
-        torch.cuda.synchronize()
-        churn["cudaMallocAsync"] = allocator_churn(lib, rt, dev, sp, args.churn_ops, arm="cudaMallocAsync")
-        torch.cuda.synchronize()
-        torch.cuda.empty_cache()
-        churn["torch_caching_allocator"] = allocator_churn(lib, rt, dev, sp, args.churn_ops, arm="torch")
-        torch.cuda.synchronize()
-        torch.cuda.empty_cache()
+def functor_section(c):
+    """out = bf16(a * sigmoid(a) * b * 0.5) over 2^30 elements (ahead-of-time kernel and the same functor through
+    NVRTC), and the bf16 -> MXFP8 functor over the same input."""
+    import numpy as np
+    from l2_torch_alloc_b200 import functors
+    torch, lib, sa = c.torch, c.lib, c.sa
+    n = FUNCTOR_ELEMS
+    a, b, o = c.alloc(2 * n), c.alloc(2 * n), c.alloc(2 * n)
+    g2 = torch.Generator(device="cuda").manual_seed(0xB200 + 4)
+    chunk = 1 << 27
+    for off in range(0, n, chunk):
+        for buf in (a, b):
+            t = torch.randn(chunk, dtype=torch.float32, device="cuda", generator=g2).to(torch.bfloat16)
+            lib.sideaware_memcpy(buf + 2 * off, t.data_ptr(), 2 * chunk, c.dev, c.sp)
+    torch.cuda.synchronize()
+    kid = sa.create_kernel(functors.silu_mul_bf16())
+    scale_bits = int(np.float32(0.5).view(np.int32))
+    f_jit = lambda: lib.sideaware_elementwise(kid, 2 * n, o, None, None, None, a, b, None, None, None, scale_bits, 0, 0, c.dev, c.sp)  # noqa: E731
+    f_aot = lambda: lib.sideaware_silu_mul_bf16(o, a, b, 0.5, n, c.dev, c.sp)  # noqa: E731
+    cfg = "bf16 2^30 elements, three side-tagged buffers"
+    functor = {"algorithmic_bytes": 6 * n, "config": cfg}
+    entries = [c.kernel_entry("sa_silu_mul_kernel", cfg, 6 * n, f_aot, 10, 2),
+               c.kernel_entry("sideaware_elementwise (NVRTC, silu-mul functor)", cfg, 6 * n, f_jit, 10, 2)]
+    for name, e in zip(("aot", "nvrtc"), entries):
+        functor[f"{name}_aware"] = {"gbs": e["event_per_launch_gbs"], "ms": e["event_per_launch_ms"], "back_to_back_gbs": e["achieved"]}
+    sa.set_placement("unaware")
+    for name, f in (("aot", f_aot), ("nvrtc", f_jit)):
+        _, ea = time_launches(torch, f, 10, 2, None, per_launch=True)
+        functor[f"{name}_unaware"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea)}
+    sa.set_placement("aware")
+    functor["frac_of_peak"] = entries[0]["frac"]
 
-    line = None
-    if ranks.rank == 0:
+    # bf16 -> MXFP8: 2 bytes read, 1 byte + 1/32 byte written per element; the output reuses `o`, the scales `b`
+    kid_mx = sa.create_kernel(functors.mxfp8_quantize_bf16())
+    mx_bytes = 2 * n + n + n // 32
+    f_mx = lambda: lib.sideaware_elementwise(kid_mx, 2 * n, o, None, None, None, a, None, None, None, b, n // 8, 0, 0, c.dev, c.sp)  # noqa: E731
+    mx_cfg = "bf16 -> E4M3 + E8M0 block scales, 2^30 elements"
+    entries.append(c.kernel_entry("sideaware_elementwise (NVRTC, MXFP8 functor)", mx_cfg, mx_bytes, f_mx, 10, 2))
+    sa.set_placement("unaware")
+    _, ea = time_launches(torch, f_mx, 10, 2, None, per_launch=True)
+    sa.set_placement("aware")
+    functor["mxfp8"] = {"algorithmic_bytes": mx_bytes, "config": mx_cfg, "aware_gbs": entries[2]["event_per_launch_gbs"],
+                        "aware_back_to_back_gbs": entries[2]["achieved"], "unaware_gbs": gbs(mx_bytes, statistics.mean(ea))}
+    for buf in (a, b, o):
+        c.free(buf, 2 * n)
+    # torch eager F.silu(a) * b * 0.5 on torch-allocated tensors of the same size, as a baseline
+    ta = torch.empty(n, dtype=torch.bfloat16, device="cuda").normal_(generator=g2)
+    tb = torch.empty(n, dtype=torch.bfloat16, device="cuda").normal_(generator=g2)
+    _, ea = time_launches(torch, lambda: torch.nn.functional.silu(ta) * tb * 0.5, 5, 2, None, per_launch=True)
+    functor["torch_eager"] = {"gbs": gbs(6 * n, statistics.mean(ea)), "ms": statistics.mean(ea),
+                              "note": "three kernels with bf16 temporaries; GB/s counts the same 6 bytes per element"}
+    if c.ranks.world == 1 and not c.args.no_torch_compile:
+        functor["torch_compile"] = compiled_baseline(torch, lambda: torch.nn.functional.silu(ta) * tb * 0.5, 6 * n)
+    del ta, tb
+    if sa.error_count():
+        functor["errors"] = sa.last_error()
+    return functor, entries
+
+
+def churn_section(c):
+    """The allocator churn of the benchmark configuration, two ways: through torch.empty under the pluggable allocator
+    in a process of its own (what the configuration names), and by calling the two entry points directly from here.
+    Beside them the same sequence on cudaMallocAsync and on torch's own caching allocator."""
+    ops = c.args.churn_ops
+    c.lib.sideaware_release_unused()
+    c.torch.cuda.synchronize()
+    churn = {"ops": ops, "sizes": "log-uniform 4 KiB .. 2 GiB, rounded up to 16 B; live set capped at 32 GiB"}
+    direct = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops)
+    direct["stats"] = c.sa.stats()
+    # the same sequence again with what the first pass mapped still mapped: the steady state of a program
+    # whose sizes repeat (no driver calls at all if every request finds a free run)
+    before = c.sa.stats()
+    second = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops)
+    after = c.sa.stats()
+    second["handles_created"] = after["handles_created"] - before["handles_created"]
+    second["served_from_mapped_runs"] = after["reuse_hits"] - before["reuse_hits"]
+    second["large_allocs"] = after["large_allocs"] - before["large_allocs"]
+    churn["sideaware_direct_calls"] = direct
+    churn["sideaware_direct_calls_second_pass"] = second
+    churn["driver_call_times"] = c.sa.driver_call_times()
+    c.lib.sideaware_release_unused()
+    c.torch.cuda.synchronize()
+    churn["cudaMallocAsync"] = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops, arm="cudaMallocAsync")
+    c.torch.cuda.synchronize()
+    c.torch.cuda.empty_cache()
+    # torch routes, each in a fresh process (the pluggable allocator has to be installed before the first allocation);
+    # this process keeps only its context while they run
+    churn["sideaware_via_torch_pluggable_allocator"] = run_script("allocator_churn_script.py", "pluggable", str(ops), timeout=1200)
+    churn["torch_caching_allocator"] = run_script("allocator_churn_script.py", "torch", str(ops), timeout=1200)
+    return churn
+
+
+def run_ours(args, ranks):
+    c = Ctx(args, ranks)
+    torch, lib = c.torch, c.lib
+    first = ranks.rank == 0
+    value, worst_ms, roofline, memcpy_entry, clocks, launches = headline_memcpy(c)
+    e2e = e2e_memcpy(c)
+    limits = comparison = power = sweep = None
+    if first:
+        limits = pcie_limits(c)
+        e2e["limit"] = dict(limits, bound=f"{2 * limits['both_directions_each_gbs']:.1f} GB/s for a step that moves its bytes "
+                                         "host -> device and device -> host at the same time")
+        comparison = comparison_memcpy(c)
+        if ranks.world == 1 and args.power_seconds > 0:
+            power = power_section(c)
+        sweep = sweep_memcpy(c)
+    c.free(c.src, MEMCPY_BYTES)
+    c.free(c.dst, MEMCPY_BYTES)
+    del c.seed_t
+    torch.cuda.synchronize()
+
+    rope, rope_entries = rope_section(c)
+    functor, functor_entries = functor_section(c) if first else (None, [])
+    roofline["kernels"] = [memcpy_entry] + rope_entries + functor_entries
+
+    churn = ref_mem = ref_rope = None
+    if first and ranks.world == 1:
+        if args.churn_ops > 0:
+            churn = churn_section(c)
+        if not args.no_reference_library:
+            lib.sideaware_release_unused()
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            ref_mem, ref_rope = reference_gpu_library(c)
+    if comparison is not None and ref_mem:
+        comparison.update(ref_mem)
+
+    if first:
         cpu = None
         if ranks.world == 1:
             threads = os.cpu_count() or 1
-            v, times = cpu_memcpy_gbs(MEMCPY_BYTES, 12, threads)
+            v, _ = cpu_memcpy_gbs(MEMCPY_BYTES, 12, threads)
             v1, _ = cpu_memcpy_gbs(MEMCPY_BYTES, 4, 1)
             cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
                    "sample": f"12 x 1 GiB libc memcpy over {threads} threads (the reference has no CPU memcpy)",
                    "one_thread_gbs": v1, "rope": cpu_rope_reference()}
+        # Key order matters to whoever keeps only the end of the line: the long sweep goes early, the summaries last.
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": ranks.world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": worst_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": "memcpy 1 GiB uint8 (seeded uniform random bytes) via sideaware_malloc_auto + sideaware_memcpy",
-                       "bytes": MEMCPY_BYTES, "l2": "inputs larger than L2 (2 GiB touched per step vs 126 MB)",
-                       "parallelism": f"{ranks.world} independent replicas, no collective"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * ranks.world,
-            "clocks": clocks.report(), "topology": summary, "rope": rope, "functor": functor,
-            "allocator_churn": churn, **extra,
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": bench_config(ranks.world),
+            "path": "sideaware_malloc_auto + sideaware_memcpy through the C ABI",
+            "memcpy_sweep": sweep, "power": power,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * ranks.world,
+            "clocks": clocks, "topology": c.summary,
+            "rope": rope, "functor": functor, "allocator_churn": churn,
+            "memcpy_comparison": comparison, "rope_comparison": ref_rope,
         }
         print(json.dumps(line), flush=True)
     ranks.close()
@@ -799,8 +1029,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-torch-compile", action="store_true", help="skip the torch.compile comparison lines")
-    ap.add_argument("--churn-ops", type=int, default=5000,
-                    help="allocator churn operations (N = 1 only; 0 = skip; the full configuration is 10000)")
+    ap.add_argument("--churn-ops", type=int, default=10000,
+                    help="allocator churn operations (N = 1 only; 0 = skip; 10000 is the benchmark configuration)")
+    ap.add_argument("--no-reference-library", action="store_true",
+                    help="skip the comparison runs of the reference's own GPU library (oracle/_ref, N = 1 only)")
     ap.add_argument("--power-seconds", type=float, default=2.0, help="length of each power sampling loop (0 = skip)")
     ap.add_argument("--check-ranks", action="store_true",
                     help="exercise only the rank plumbing (barrier, max/sum over ranks, rank 0 prints); needs no GPU")

@@ -193,15 +193,22 @@ SA_API void sideaware_elementwise(int kernel_id, size_t num_bytes,
         return;
     }
     int groups = parallel_groups > 0 ? parallel_groups : sa_jit_default_groups(kernel_id);
+    bool misaligned = ((uintptr_t)in0 % kSaPageBytes) || ((uintptr_t)out0 % kSaPageBytes);
+    bool wide = misaligned || num_bytes >= (2ull << 30); // same rule as sideaware.cu:1386-1388
+    std::string why;
+    // a header may bound its block size (LAUNCH_BOUNDS) below the four 256-thread groups of the default launch
+    const int max_threads = sa_jit_max_threads(dev, kernel_id, wide, &why);
+    if (max_threads < 256) {
+        sa_set_error("sideaware_elementwise(kernel %d): %s", kernel_id, why.empty() ? "the functor cannot run 256 threads per block" : why.c_str());
+        return;
+    }
+    if (groups > max_threads / 256) groups = max_threads / 256;
     // geometry is redone inside the kernel for whichever array it moves as 16-byte vectors;
     // the host only needs the size to pick grid and ticket length
     const void* track = in0 ? in0 : out0;
     if (!sa_prepare_launch(dev, stream, (uint64_t)track, num_vecs, groups, forced_per_side, false, &s, &grid, &threads)) return;
-    bool misaligned = ((uintptr_t)in0 % kSaPageBytes) || ((uintptr_t)out0 % kSaPageBytes);
-    bool wide = misaligned || num_bytes >= (2ull << 30); // same rule as sideaware.cu:1386-1388
     void* outs[4] = {out0, out1, out2, out3};
     const void* ins[4] = {in0, in1, in2, in3};
-    std::string why;
     e = sa_jit_launch(dev, kernel_id, wide, s, grid, threads, num_vecs, outs, ins, sideband_memory, sideband_value,
                       (cudaStream_t)stream, &why);
     if (e != cudaSuccess) sa_set_error("sideaware_elementwise(kernel %d): %s", kernel_id, why.c_str());

@@ -306,7 +306,7 @@ bool sa_prepare_launch(SaDevice* dev, void* stream, uint64_t track_addr, uint64_
     if (forced_per_side > 0 && 2 * forced_per_side < g) g = 2 * forced_per_side;
     s->dc_per_ticket = 0;
     sa_sched_geometry(*s, track_addr, num_vecs, (uint32_t)(g * warps / 2));
-    sa_sched_grid(*s, g, warps, &g);
+    sa_sched_grid(*s, g, warps, &g, dev->topo.count[0], dev->topo.count[1]);
     bool overlap = false;
     s->tickets = sa_probe_ticket_slot(dev->probe, stream, &overlap);
     if (!s->tickets) {

@@ -37,6 +37,7 @@ void load() {
     SA_SYM(ModuleLoadData, "cuModuleLoadData");
     SA_SYM(ModuleUnload, "cuModuleUnload");
     SA_SYM(ModuleGetFunction, "cuModuleGetFunction");
+    SA_SYM(FuncGetAttribute, "cuFuncGetAttribute");
     SA_SYM(LaunchKernel, "cuLaunchKernel");
     SA_SYM(LaunchKernelEx, "cuLaunchKernelEx");
 #undef SA_SYM

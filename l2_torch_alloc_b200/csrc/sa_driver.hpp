@@ -20,6 +20,7 @@ struct SaDriver {
     CUresult (*ModuleLoadData)(CUmodule*, const void*);
     CUresult (*ModuleUnload)(CUmodule);
     CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*);
+    CUresult (*FuncGetAttribute)(int*, CUfunction_attribute, CUfunction);
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                              CUstream, void**, void**);
     CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**);

@@ -86,6 +86,7 @@ struct SaJitDeviceCache {
     struct Entry {
         CUmodule mod[2] = {nullptr, nullptr};
         CUfunction fn[2] = {nullptr, nullptr};
+        int max_threads[2] = {0, 0};
         std::string error[2];
     };
     std::vector<Entry> entries;
@@ -243,6 +244,20 @@ static CUfunction get_function(SaDevice* dev, int id, bool wide, std::string* wh
         return nullptr;
     }
     return e.fn[v];
+}
+
+int sa_jit_max_threads(SaDevice* dev, int id, bool wide, std::string* why) {
+    CUfunction fn = get_function(dev, id, wide, why);
+    if (!fn) return 0;
+    std::lock_guard<std::mutex> lock(dev->jit_mu);
+    int& cached = dev->jit->entries[id].max_threads[wide ? 1 : 0];
+    if (cached == 0) {
+        int v = 0;
+        CUresult r = dev->drv->FuncGetAttribute(&v, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, fn);
+        if (r != CUDA_SUCCESS || v <= 0) { *why = "cuFuncGetAttribute: " + sa_cu_error(dev->drv, r); return 0; }
+        cached = v;
+    }
+    return cached;
 }
 
 bool sa_jit_precompile(SaDevice* dev, int id, std::string* why) {

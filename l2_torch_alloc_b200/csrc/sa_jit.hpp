@@ -27,6 +27,9 @@ int sa_jit_default_groups(int id);
 cudaError_t sa_jit_launch(SaDevice* dev, int id, bool wide, const SaSched& sched, int grid, int threads,
                           unsigned long long num_vecs, void* const out[4], const void* const in[4],
                           void* mem, int val, cudaStream_t stream, std::string* why);
+// Most threads per block the compiled functor can be launched with (its LAUNCH_BOUNDS and register use decide);
+// compiles on first use.  0 (and *why) on failure.
+int sa_jit_max_threads(SaDevice* dev, int id, bool wide, std::string* why);
 // Compiles both variants now; false (and *why) on failure.
 bool sa_jit_precompile(SaDevice* dev, int id, std::string* why);
 // Compiles `header` for sm_100a without loading it (no GPU needed); for build-time checks.

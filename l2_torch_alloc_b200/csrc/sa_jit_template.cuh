@@ -137,6 +137,88 @@ struct SaJitArgs {
     int val;
 };
 
+struct SaJitArrays {
+    sa_pack<o0>* po0;
+    sa_pack<o1>* po1;
+    sa_pack<o2>* po2;
+    sa_pack<o3>* po3;
+    const sa_pack<i0>* pi0;
+    const sa_pack<i1>* pi1;
+    const sa_pack<i2>* pi2;
+    const sa_pack<i3>* pi3;
+};
+
+// One 4 KiB chunk.  Which of its 256 vectors exist (all of them, except in the array's first and last chunk)
+// is worked out once per chunk as a chunk-local range, so the per-vector test is two 32-bit comparisons.
+__device__ __forceinline__ void sa_process_chunk(const SaSched& s, const SaJitArgs& a, const SaJitArrays& p,
+                                                 sa_u64 first_vec, sa_u32 lane) {
+    sa_pack<o0>* const po0 = p.po0;
+    sa_pack<o1>* const po1 = p.po1;
+    sa_pack<o2>* const po2 = p.po2;
+    sa_pack<o3>* const po3 = p.po3;
+    const sa_pack<i0>* const pi0 = p.pi0;
+    const sa_pack<i1>* const pi1 = p.pi1;
+    const sa_pack<i2>* const pi2 = p.pi2;
+    const sa_pack<i3>* const pi3 = p.pi3;
+    const size_type v0 = (size_type)(first_vec - s.lead) + (size_type)lane; // may be "negative" in the first chunk
+    const sa_u32 lo = first_vec >= s.lead ? 0u : (sa_u32)(s.lead - first_vec);
+    const sa_u32 hi = first_vec + SA_CHUNK_VECS <= s.end ? SA_CHUNK_VECS : (sa_u32)(s.end - first_vec);
+#pragma unroll 1
+    for (int b = 0; b < SA_VEC_PER_LANE / sa_batch; ++b) {
+        bool live[sa_batch];
+        sa_pack<i0> r0[sa_batch];
+        sa_pack<i1> r1[sa_batch];
+        sa_pack<i2> r2[sa_batch];
+        sa_pack<i3> r3[sa_batch];
+#pragma unroll
+        for (int j = 0; j < sa_batch; ++j) {
+            const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
+            const sa_u32 in_chunk = (sa_u32)((b * sa_batch + j) * 32) + lane;
+            live[j] = in_chunk >= lo && in_chunk < hi;
+            if (live[j]) {
+                size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
+                live[j] = !indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
+                if (live[j]) {
+                    sa_load<input_evict[0]>(r0[j], pi0, x0);
+                    sa_load<input_evict[1]>(r1[j], pi1, x1);
+                    sa_load<input_evict[2]>(r2[j], pi2, x2);
+                    sa_load<input_evict[3]>(r3[j], pi3, x3);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < sa_batch; ++j) {
+            if (live[j]) {
+                const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
+                sa_pack<o0> w0;
+                sa_pack<o1> w1;
+                sa_pack<o2> w2;
+                sa_pack<o3> w3;
+                vector_op(vidx, vec_size, w0.v, w1.v, w2.v, w3.v, r0[j].v, r1[j].v, r2[j].v, r3[j].v, a.mem, a.val);
+                sa_store(po0, vidx, w0);
+                sa_store(po1, vidx, w1);
+                sa_store(po2, vidx, w2);
+                sa_store(po3, vidx, w3);
+            }
+        }
+#ifdef DISCARD_INPUTS
+        // after the stores of the batch; the input positions are computed again rather than kept
+#pragma unroll
+        for (int j = 0; j < sa_batch; ++j) {
+            if (live[j]) {
+                const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
+                size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
+                indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
+                sa_discard(pi0, x0, input_discard[0]);
+                sa_discard(pi1, x1, input_discard[1]);
+                sa_discard(pi2, x2, input_discard[2]);
+                sa_discard(pi3, x3, input_discard[3]);
+            }
+        }
+#endif
+    }
+}
+
 extern "C" __global__ LAUNCH_BOUNDS void sideaware_elementwise(const __grid_constant__ SaSched launch,
                                                                const __grid_constant__ SaSideTable sides,
                                                                const __grid_constant__ SaJitArgs a) {
@@ -147,72 +229,18 @@ extern "C" __global__ LAUNCH_BOUNDS void sideaware_elementwise(const __grid_cons
     if (FORCE_WRONG_SIDE && s.hash) s.placement = SA_PLACE_WRONG;
     if (FORCE_RANDOM_SIDE) s.placement = SA_PLACE_UNAWARE;
 
-    sa_pack<o0>* const po0 = (sa_pack<o0>*)a.out[0];
-    sa_pack<o1>* const po1 = (sa_pack<o1>*)a.out[1];
-    sa_pack<o2>* const po2 = (sa_pack<o2>*)a.out[2];
-    sa_pack<o3>* const po3 = (sa_pack<o3>*)a.out[3];
-    const sa_pack<i0>* const pi0 = (const sa_pack<i0>*)a.in[0];
-    const sa_pack<i1>* const pi1 = (const sa_pack<i1>*)a.in[1];
-    const sa_pack<i2>* const pi2 = (const sa_pack<i2>*)a.in[2];
-    const sa_pack<i3>* const pi3 = (const sa_pack<i3>*)a.in[3];
     const sa_u32 lane = sa_lane();
 
+    SaJitArrays arrays;
+    arrays.po0 = (sa_pack<o0>*)a.out[0];
+    arrays.po1 = (sa_pack<o1>*)a.out[1];
+    arrays.po2 = (sa_pack<o2>*)a.out[2];
+    arrays.po3 = (sa_pack<o3>*)a.out[3];
+    arrays.pi0 = (const sa_pack<i0>*)a.in[0];
+    arrays.pi1 = (const sa_pack<i1>*)a.in[1];
+    arrays.pi2 = (const sa_pack<i2>*)a.in[2];
+    arrays.pi3 = (const sa_pack<i3>*)a.in[3];
     sa_for_each_chunk(s, sides, [&](sa_u64 first_vec) {
-        const bool whole = first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end;
-        const size_type v0 = (size_type)(first_vec - s.lead) + (size_type)lane; // may be "negative" in the first chunk
-#pragma unroll 1
-        for (int b = 0; b < SA_VEC_PER_LANE / sa_batch; ++b) {
-            bool live[sa_batch];
-            sa_pack<i0> r0[sa_batch];
-            sa_pack<i1> r1[sa_batch];
-            sa_pack<i2> r2[sa_batch];
-            sa_pack<i3> r3[sa_batch];
-#pragma unroll
-            for (int j = 0; j < sa_batch; ++j) {
-                const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
-                live[j] = whole || (first_vec + (sa_u64)((b * sa_batch + j) * 32) + lane >= s.lead &&
-                                    first_vec + (sa_u64)((b * sa_batch + j) * 32) + lane < s.end);
-                if (live[j]) {
-                    size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
-                    live[j] = !indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
-                    if (live[j]) {
-                        sa_load<input_evict[0]>(r0[j], pi0, x0);
-                        sa_load<input_evict[1]>(r1[j], pi1, x1);
-                        sa_load<input_evict[2]>(r2[j], pi2, x2);
-                        sa_load<input_evict[3]>(r3[j], pi3, x3);
-                    }
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < sa_batch; ++j) {
-                if (live[j]) {
-                    const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
-                    sa_pack<o0> w0;
-                    sa_pack<o1> w1;
-                    sa_pack<o2> w2;
-                    sa_pack<o3> w3;
-                    vector_op(vidx, vec_size, w0.v, w1.v, w2.v, w3.v, r0[j].v, r1[j].v, r2[j].v, r3[j].v, a.mem, a.val);
-                    sa_store(po0, vidx, w0);
-                    sa_store(po1, vidx, w1);
-                    sa_store(po2, vidx, w2);
-                    sa_store(po3, vidx, w3);
-                }
-            }
-#ifdef DISCARD_INPUTS
-            // after the stores of the batch; the input positions are computed again rather than kept
-#pragma unroll
-            for (int j = 0; j < sa_batch; ++j) {
-                if (live[j]) {
-                    const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
-                    size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
-                    indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
-                    sa_discard(pi0, x0, input_discard[0]);
-                    sa_discard(pi1, x1, input_discard[1]);
-                    sa_discard(pi2, x2, input_discard[2]);
-                    sa_discard(pi3, x3, input_discard[3]);
-                }
-            }
-#endif
-        }
+        sa_process_chunk(s, a, arrays, first_vec, lane);
     });
 }

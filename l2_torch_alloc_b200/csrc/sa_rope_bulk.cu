@@ -108,6 +108,11 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
     // cos/sin position of this lane's vectors inside a head: fixed when a head is a power-of-two
     // number of vectors that divides the 32-lane stride (rows are whole heads, so it survives a row change)
     const bool pos_fixed = sh.head_shift >= 0 && sh.vecs_per_head <= 32u;
+    // In that case the cos/sin entries of a chunk (its row's token and the next one) are fetched when the chunk's
+    // load is issued and wait in registers, in the order of the ring, until the chunk is rotated: their latency
+    // is hidden behind the data's.  Slot 0 belongs to the oldest chunk in flight.
+    constexpr int kQueue = (int)kLoadsInFlight + 1;
+    RopeTab<BF16> tabs[kQueue][2];
 
     // wait for the oldest chunk in flight, rotate it in shared memory, send it back
     auto retire = [&]() {
@@ -118,7 +123,6 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
             const Runs runs = chunk_runs(sh, info.r0);
             const uint32_t stage = my_stage0 + st * SA_BULK_CHUNK_BYTES;
             const uint32_t tok1 = info.tok0 + 1u == sh.T ? 0u : info.tok0 + 1u;
-            const uint32_t pos_lane = (info.r0 + lane) & (sh.vecs_per_head - 1u);
             // ordinary shared-memory accesses, 16 bytes per lane: the eight loads first, then arithmetic and stores
             uint4* const sp = reinterpret_cast<uint4*>(stage_mem + (size_t)(warp * S + st) * SA_BULK_CHUNK_BYTES) + lane;
             uint4 v[SA_VEC_PER_LANE];
@@ -127,22 +131,38 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
                 const uint32_t i = lane + 32u * k;
                 if (i < runs.a_end || (i >= runs.b_begin && i < runs.b_end)) v[k] = sp[32 * k];
             }
-            uint32_t have_tok = 0xffffffffu;
-            RopeTab<BF16> tab;
+            if (pos_fixed) {
+                const RopeTab<BF16> ta = tabs[0][0], tb = tabs[0][1];
+                if (runs.b_begin >= runs.b_end) { // the usual case: the chunk lies inside one row
 #pragma unroll
-            for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
-                const uint32_t i = lane + 32u * k;
-                const bool in_a = i < runs.a_end;
-                const bool in_b = i >= runs.b_begin && i < runs.b_end;
-                if (in_a || in_b) {
-                    const uint32_t tok = in_a ? info.tok0 : tok1;
-                    if (!pos_fixed || tok != have_tok) {
-                        const uint32_t r = in_a ? info.r0 + i : i - runs.b_begin;
-                        const uint32_t pos = pos_fixed ? pos_lane : (r % sh.vecs_per_head);
-                        tab = rope_load_tab<BF16>(table + tok * sh.tab_vecs_per_token + pos * sh.tab_vecs_per_vec, sh.inverse != 0);
-                        have_tok = tok;
+                    for (int k = 0; k < SA_VEC_PER_LANE; ++k)
+                        if (lane + 32u * k < runs.a_end) sp[32 * k] = rope_apply<BF16>(v[k], ta);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                        const uint32_t i = lane + 32u * k;
+                        if (i < runs.a_end) sp[32 * k] = rope_apply<BF16>(v[k], ta);
+                        else if (i >= runs.b_begin && i < runs.b_end) sp[32 * k] = rope_apply<BF16>(v[k], tb);
                     }
-                    sp[32 * k] = rope_apply<BF16>(v[k], tab);
+                }
+            } else {
+                uint32_t have = 0xffffffffu;
+                RopeTab<BF16> tab;
+#pragma unroll
+                for (int k = 0; k < SA_VEC_PER_LANE; ++k) {
+                    const uint32_t i = lane + 32u * k;
+                    const bool in_a = i < runs.a_end;
+                    const bool in_b = i >= runs.b_begin && i < runs.b_end;
+                    if (in_a || in_b) {
+                        const uint32_t tok = in_a ? info.tok0 : tok1;
+                        const uint32_t r = in_a ? info.r0 + i : i - runs.b_begin;
+                        const uint32_t idx = tok * sh.tab_vecs_per_token + (r % sh.vecs_per_head) * sh.tab_vecs_per_vec;
+                        if (idx != have) {
+                            tab = rope_load_tab<BF16>(table + idx, sh.inverse != 0);
+                            have = idx;
+                        }
+                        sp[32 * k] = rope_apply<BF16>(v[k], tab);
+                    }
                 }
             }
             sa_fence_async_shared(); // this lane's shared-memory writes, before the bulk store reads them
@@ -157,6 +177,11 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
             atomicAdd_system(wait_errors, 1u);
         }
         sa_ring_retire(ring, S, arrived);
+#pragma unroll
+        for (int i = 0; i + 1 < kQueue; ++i) {
+            tabs[i][0] = tabs[i + 1][0];
+            tabs[i][1] = tabs[i + 1][1];
+        }
     };
 
     sa_for_each_chunk(s, sides, [&](uint64_t first_vec) {
@@ -168,6 +193,20 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
             const Runs runs = chunk_runs(sh, r0);
             const uint32_t vecs = runs.a_end + (runs.b_end - runs.b_begin);
             if (vecs == 0u) return; // nothing but V heads in this chunk
+            const uint32_t slot = sa_ring_in_flight(ring); // chunks ahead of this one in the ring
+            const uint32_t tok0 = (uint32_t)(row0 % sh.T);
+            if (pos_fixed) {
+                const uint32_t pos = ((r0 + lane) & (sh.vecs_per_head - 1u)) * sh.tab_vecs_per_vec;
+                const uint32_t tok1 = tok0 + 1u == sh.T ? 0u : tok0 + 1u;
+                const RopeTab<BF16> ta = rope_load_tab<BF16>(table + tok0 * sh.tab_vecs_per_token + pos, sh.inverse != 0);
+                const RopeTab<BF16> tb = rope_load_tab<BF16>(table + tok1 * sh.tab_vecs_per_token + pos, sh.inverse != 0);
+#pragma unroll
+                for (int i = 0; i < kQueue; ++i)
+                    if ((uint32_t)i == slot) {
+                        tabs[i][0] = ta;
+                        tabs[i][1] = tb;
+                    }
+            }
             const uint32_t st = sa_ring_issue(ring, S);
             if (lane == 0) {
                 // the store that last used this stage (S chunks ago) must have read it
@@ -179,7 +218,7 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
                 StageInfo info;
                 info.first_vec = first_vec;
                 info.r0 = r0;
-                info.tok0 = (uint32_t)(row0 % sh.T);
+                info.tok0 = tok0;
                 my_infos[st] = info;
             }
             __syncwarp(); // the stage's info is visible to the lanes that will rotate it

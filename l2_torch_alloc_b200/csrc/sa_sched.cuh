@@ -51,7 +51,8 @@ struct SaSched {
     sa_u32 reverse;         // walk double chunks from the end
     sa_u32 total_blocks;    // blocks of the grid (the last one to finish rewinds the tickets)
     sa_u32 active_warps;    // warps per block that take part (small arrays do not need all of them)
-    sa_u32 share;           // tickets every active warp takes from its block's opening batch (no atomics)
+    sa_u32 share;           // most tickets an active warp takes from its block's opening batch (no atomics)
+    sa_u32 opening[2];      // tickets a block on side 0 / side 1 takes with its opening atomic (<= active_warps * share)
     sa_u32 dynamic;         // 1: after the share, warps claim single tickets for themselves (large arrays)
     sa_u32 overlap;         // host side only: 1 = the launch may begin while its predecessor on the stream drains
 };
@@ -128,24 +129,39 @@ SA_HD void sa_sched_geometry(SaSched& s, sa_u64 addr, sa_u64 num_vecs, sa_u32 wa
 //    would cost more than the copy), spread over all blocks with only as many warps each as
 //    there is work for; tiny ones get one block per ticket.
 // Whatever an uneven SM split or a busy SM leaves over is swept up block-wide at the end.
-SA_HD void sa_sched_grid(SaSched& s, int max_blocks, int warps, int* grid) {
+SA_HD void sa_sched_grid(SaSched& s, int max_blocks, int warps, int* grid, int sms_side0 = -1, int sms_side1 = -1) {
     sa_u64 total = 2ull * s.num_tickets;
     int g = max_blocks < 1 ? 1 : max_blocks;
     if (total < (sa_u64)g) g = (int)(total ? total : 1);
-    const sa_u64 blocks_side = (sa_u64)(g + 1) / 2;
-    const sa_u64 warps_side = blocks_side * (sa_u64)warps;
+    // blocks that will work for each side: the SM counts of the sides when the grid has one block per SM
+    // (the two dies need not have equally many SMs), else half the grid each
+    sa_u64 blocks[2] = {(sa_u64)(g + 1) / 2, (sa_u64)(g + 1) / 2};
+    if (sms_side0 > 0 && sms_side1 > 0 && sms_side0 + sms_side1 == g) {
+        blocks[0] = (sa_u64)sms_side0;
+        blocks[1] = (sa_u64)sms_side1;
+    }
+    const sa_u64 fewer = blocks[0] < blocks[1] ? blocks[0] : blocks[1];
     const sa_u64 M = s.num_tickets;
-    if (M >= 4 * warps_side) {
+    if (M >= 4 * fewer * (sa_u64)warps) {
         s.active_warps = (sa_u32)warps;
-        sa_u64 share = (M * 6 / 10) / warps_side;
+        const sa_u64 more = blocks[0] < blocks[1] ? blocks[1] : blocks[0];
+        sa_u64 share = (M * 6 / 10) / (more * (sa_u64)warps);
         s.share = (sa_u32)(share < 1 ? 1 : share);
+        s.opening[0] = s.opening[1] = s.share * s.active_warps;
         s.dynamic = 1;
     } else {
-        sa_u64 per_block = (M + blocks_side - 1) / blocks_side;
-        if (per_block < 1) per_block = 1;
-        sa_u64 active = per_block > (sa_u64)warps ? (sa_u64)warps : per_block;
+        // everything is dealt out at the start: a block of side i takes its even share of that side's tickets
+        sa_u64 per_block[2], most = 1;
+        for (int i = 0; i < 2; ++i) {
+            per_block[i] = (M + blocks[i] - 1) / blocks[i];
+            if (per_block[i] < 1) per_block[i] = 1;
+            if (per_block[i] > most) most = per_block[i];
+        }
+        sa_u64 active = most > (sa_u64)warps ? (sa_u64)warps : most;
         s.active_warps = (sa_u32)active;
-        s.share = (sa_u32)((per_block + active - 1) / active);
+        s.share = (sa_u32)((most + active - 1) / active);
+        s.opening[0] = (sa_u32)per_block[0];
+        s.opening[1] = (sa_u32)per_block[1];
         s.dynamic = 0;
     }
     s.total_blocks = (sa_u32)g;
@@ -170,8 +186,8 @@ SA_D sa_u32 sa_lane() { return threadIdx.x & 31u; }
 //
 // Same-address atomics are the scarce resource (an L2 slice retires one every few
 // cycles), so they are kept few and off the critical path:
-//  1. a block opens with ONE atomic that takes share x active_warps tickets; warp w works on
-//     tickets base + w, base + w + active_warps, ... (neighbouring warps, neighbouring memory);
+//  1. a block opens with ONE atomic that takes opening[side] tickets (at most share x active_warps);
+//     warp w works on tickets base + w, base + w + active_warps, ... (neighbouring warps, neighbouring memory);
 //  2. for large arrays each warp then claims single tickets for itself, always one ahead of
 //     the ticket it is working on (the result is only looked at after that ticket is done);
 //  3. leftovers of both sides (uneven SM split, a busy SM) are taken by the block as a whole,
@@ -204,7 +220,7 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         sa_drained = 0u;
-        sa_batch = atomicAdd(own, s.active_warps * s.share);
+        sa_batch = atomicAdd(own, s.opening[my_side]);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
@@ -217,11 +233,12 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
     for (;;) {
         sa_u32 t = none, side = my_side;
         if (phase == 0u) {
-            if (dealt == s.share) {
+            const sa_u32 mine = dealt * s.active_warps + warp; // position in the block's opening batch
+            if (dealt == s.share || mine >= s.opening[my_side]) {
                 phase = s.dynamic ? 1u : 2u;
                 continue;
             }
-            t = base + dealt * s.active_warps + warp;
+            t = base + mine;
             ++dealt;
             if (s.dynamic && dealt == s.share) pending = claim_issue(); // overlaps the last dealt ticket
         } else if (phase == 1u) {

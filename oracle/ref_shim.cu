@@ -22,3 +22,14 @@ REF_EXPORT void ref_apply_rotary_emb_backward(float* dinp, const float* dout, co
                                               int B, int T, int n_head, int head_dim) {
     apply_rotary_emb_backward(dinp, dout, inp, table, B, T, n_head, head_dim);
 }
+
+// llm.c's naive in-place RoPE kernel (example_llmc_rope.cu:89-121), launched as the reference's launcher does
+// (:124-130) but with the query / key-value head counts passed through, on a caller-given stream.  Used only as
+// the "naive GPU kernel" line of the benchmark's comparison table.
+REF_EXPORT int ref_rope_forward_inplace_kernel1(float* inout, const float* table, int B, int T, int n_q, int n_kv,
+                                                int head_dim, int block_size, void* stream) {
+    int total_threads = B * T * (n_q + 2 * n_kv) * head_dim / 2;
+    int num_blocks = (total_threads + block_size - 1) / block_size;
+    rope_forward_inplace_kernel1<<<num_blocks, block_size, 0, (cudaStream_t)stream>>>(inout, table, B, T, n_q, n_kv, head_dim);
+    return (int)cudaGetLastError();
+}

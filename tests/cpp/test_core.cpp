@@ -82,6 +82,56 @@ static void sched_case(uint64_t addr, uint64_t num_vecs, uint32_t hash, uint32_t
     }
 }
 
+// What the blocks of one launch do with the ticket counters, block after block (one of the orders the hardware
+// may run them in): opening batch, per-warp claims, block-wide sweep of both sides.  Mirrors sa_for_each_chunk.
+static void sched_grid_replay(const SaSched& s, int grid, int blocks_on_side0, int order, std::mt19937_64& rng) {
+    const uint32_t M = s.num_tickets;
+    std::vector<uint32_t> worked[2] = {std::vector<uint32_t>(M, 0), std::vector<uint32_t>(M, 0)};
+    uint32_t counter[2] = {0, 0};
+    std::vector<int> blocks(grid);
+    for (int b = 0; b < grid; ++b) blocks[b] = b;
+    if (order == 1) std::reverse(blocks.begin(), blocks.end());
+    if (order == 2) std::shuffle(blocks.begin(), blocks.end(), rng);
+    auto work = [&](uint32_t side, uint32_t t) {
+        if (t < M) worked[side][t]++;
+    };
+    for (int b : blocks) {
+        const uint32_t my = b < blocks_on_side0 ? 0u : 1u;
+        const uint32_t base = counter[my];
+        counter[my] += s.opening[my];
+        bool drained = false;
+        for (uint32_t warp = 0; warp < s.active_warps; ++warp) {
+            for (uint32_t dealt = 0; dealt < s.share; ++dealt) {
+                const uint32_t mine = dealt * s.active_warps + warp;
+                if (mine >= s.opening[my]) break;
+                work(my, base + mine);
+            }
+            if (s.dynamic) {
+                for (;;) {
+                    if (drained) break;
+                    const uint32_t t = counter[my]++;
+                    if (t >= M) { drained = true; break; }
+                    work(my, t);
+                }
+            }
+        }
+        for (;;) { // block-wide leftovers, both sides
+            const uint32_t a = counter[my], o = counter[my ^ 1u];
+            counter[my] += s.active_warps;
+            counter[my ^ 1u] += s.active_warps;
+            if (a >= M && o >= M) break;
+            for (uint32_t warp = 0; warp < s.active_warps; ++warp) {
+                work(my, a + warp);
+                work(my ^ 1u, o + warp);
+            }
+        }
+    }
+    bool once = true;
+    for (uint32_t side = 0; side < 2; ++side)
+        for (uint32_t t = 0; t < M; ++t) once = once && worked[side][t] == 1;
+    CHECK(once);
+}
+
 static void test_sched() {
     const uint32_t hashes[] = {0x1EF000u | (1u << 21), 0xB3000u | (1u << 21), 0x1000u | (1u << 21), 0u};
     std::mt19937_64 rng(1234);
@@ -120,6 +170,23 @@ static void test_sched() {
             uint64_t dealt = (uint64_t)((grid + 1) / 2) * s.active_warps * s.share;
             if (!s.dynamic) CHECK(dealt >= s.num_tickets);
             if (s.dynamic) CHECK(dealt < s.num_tickets && s.active_warps == (uint32_t)warps);
+        }
+    }
+    // the block loop itself (sa_for_each_chunk), replayed on the host: every ticket of both sides is worked on
+    // exactly once whatever side the blocks find themselves on - one block per SM with equal or unequal
+    // sides, all blocks on one side, fewer blocks than planned for
+    for (uint64_t n : {1ull, 700ull, 512ull * 100, 1ull << 18, 1ull << 21, 1ull << 22, 3ull << 22, 1ull << 26, 1ull << 28}) {
+        for (int warps : {8, 16, 24, 32}) {
+            for (int split : {74, 70, 60, 148, 0}) {
+                SaSched s;
+                std::memset(&s, 0, sizeof(s));
+                sa_sched_geometry(s, 0x7f0000000000ull, n, 74 * warps);
+                int grid = 0;
+                sa_sched_grid(s, 148, warps, &grid, split, 148 - split);
+                CHECK(s.opening[0] <= s.active_warps * s.share && s.opening[1] <= s.active_warps * s.share);
+                CHECK(s.opening[0] >= 1 && s.opening[1] >= 1);
+                for (int order = 0; order < 3; ++order) sched_grid_replay(s, grid, split, order, rng);
+            }
         }
     }
     std::printf("sched: done\n");

@@ -20,6 +20,18 @@ from l2_torch_alloc_b200 import functors  # noqa: E402  (header texts only)
 def main():
     staged, so = sys.argv[1], sys.argv[2]
     sys.path.insert(0, staged)
+    # The wrapper keeps its torch.library.Library in a local variable of sideaware_init (example_wrapper.py:82-92).
+    # This torch version unregisters a library's operators when the Library object is collected, i.e. when
+    # sideaware_init returns.  The wrapper's text stays as it is; this harness keeps every Library it creates alive.
+    kept = []
+    original_library = torch.library.Library
+
+    class KeptLibrary(original_library):
+        def __init__(self, *a, **k):
+            super().__init__(*a, **k)
+            kept.append(self)
+
+    torch.library.Library = KeptLibrary
     import example_wrapper as ew  # the reference's file, unmodified
 
     ew.sideaware_init(so)

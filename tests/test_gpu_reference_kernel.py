@@ -25,7 +25,7 @@ def run(lib, sizes):
 
 
 @pytest.mark.skipif(not os.path.exists(REF), reason="compiled reference not present")
-def test_memcpy_not_slower_than_the_reference_kernel():
+def test_memcpy_faster_than_the_reference_kernel():
     sizes = f"{64 << 20},{1 << 30}"
     ref = run(REF, sizes)
     ours = run(OURS, sizes)
@@ -35,11 +35,11 @@ def test_memcpy_not_slower_than_the_reference_kernel():
     for n in ref["sizes"]:
         assert ref["sizes"][n]["exact"] and ours["sizes"][n]["exact"]
     one_gib = str(1 << 30)
-    assert ours["sizes"][one_gib]["gbs"] >= 0.97 * ref["sizes"][one_gib]["gbs"]
+    assert ours["sizes"][one_gib]["gbs"] > ref["sizes"][one_gib]["gbs"], "the bar is beating the reference's kernel on the same box"
 
 
 @pytest.mark.skipif(not os.path.exists(REF), reason="compiled reference not present")
-def test_rope_functor_not_slower_than_the_reference_template():
+def test_rope_faster_than_the_reference_template():
     """The same fp32 RoPE functor header through both libraries' NVRTC paths (the reference's kernel
     template vs this library's), at the reference example's shape, each checked against the oracle."""
     out = {}
@@ -52,4 +52,7 @@ def test_rope_functor_not_slower_than_the_reference_template():
         print(name, json.dumps(out[name]))
     assert out["ours"]["bit_exact"], "this library's functor path must reproduce the oracle bit for bit"
     assert out["reference"]["within_1e-6"], "the reference's fast-math JIT stays within its own tolerance"
-    assert out["ours"]["gbs"] >= 0.90 * out["reference"]["gbs"]  # separate processes, short kernel: allow run-to-run noise
+    # the bar is beating the reference's kernel on the same box: the same header through this library's template,
+    # and this library's ahead-of-time RoPE kernel on the same shape
+    assert out["ours"]["gbs"] > out["reference"]["gbs"]
+    assert out["ours"]["aot_gbs"] > out["reference"]["gbs"]
