@@ -256,7 +256,10 @@ class SideAware:
         assert out.numel() >= n and scales.numel() >= (n + 31) // 32 and scales.numel() % 4 == 0
         assert n // 8 < 2 ** 31
         kid = self.create_kernel(functors.mxfp8_quantize_bf16())
-        self.elementwise(kid, out[:n], None, None, None, x, None, None, None, scales.view(torch.int32), n // 8)
+        # the vector count tells the functor where the last, partial block ends; 0 = there is none (the common case,
+        # in which the functor skips that bookkeeping)
+        self.elementwise(kid, out[:n], None, None, None, x, None, None, None, scales.view(torch.int32),
+                         n // 8 if n % 32 else 0)
 
     def side_index_tensor(self):
         import torch

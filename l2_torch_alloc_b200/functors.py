@@ -95,9 +95,10 @@ def mxfp8_quantize_bf16() -> str:
     (elements / 8; 0 = the element count is a multiple of 32).
 
     A lane holds 8 elements, so a block is the four vectors of a lane quad and the block maximum is a
-    reduction over the quad.  Which lanes of a quad take part is worked out from the vector index and the
-    vector count, never from which lanes happen to be converged: in the last, partial block of an array
-    whose element count is not a multiple of 32 only the lanes that exist exchange values.  The input must
+    reduction over the quad.  Where the whole warp is present and every lane's block is whole, the quads
+    exchange under the full-warp mask; otherwise which lanes of a quad take part is worked out from the vector
+    index and the vector count: in the last, partial block of an array whose element count is not a multiple
+    of 32 only the lanes that exist exchange values.  The input must
     start on a 64-byte boundary (then vector 4k..4k+3 of the array are lanes 4j..4j+3 of one warp
     instruction); SideAware.mxfp8_quantize checks that.  Only the exponent of the maximum matters, so it is
     taken on the bf16 bit patterns (two elements per instruction), and the scaling is one exact
@@ -120,11 +121,13 @@ __device__ __forceinline__ unsigned sa_max_u16x2(unsigned a, unsigned b) {
     asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); // one instruction on sm_90 and later
     return d;
 }
-// maximum over the lanes of a quad that are named in `quad` (kept out of line: it runs once per array)
+// packed maximum over the lanes of a quad that are named in `quad`: arrays whose element count is not a
+// multiple of 32, and the ragged chunks at the ends of an array (kept out of line, off the common path)
 __device__ __noinline__ unsigned sa_partial_quad_max(unsigned m, unsigned quad, unsigned first) {
+    unsigned r = m;
     for (unsigned i = 0; i < 4; i++)
-        if ((quad >> (first + i)) & 1u) m = max(m, __shfl_sync(quad, m, first + i));
-    return m;
+        if ((quad >> (first + i)) & 1u) r = sa_max_u16x2(r, __shfl_sync(quad, m, first + i));
+    return r;
 }
 #define CUSTOM_VECTOR_OP
 __device__ void vector_op(size_type vec_idx, int n, o0 *out0, o1 *out1, o2 *out2, o3 *out3,
@@ -133,35 +136,44 @@ __device__ void vector_op(size_type vec_idx, int n, o0 *out0, o1 *out1, o2 *out2
     // magnitudes order like their 15-bit patterns: maximum of two elements per instruction
     unsigned m = sa_max_u16x2(sa_max_u16x2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu),
                               sa_max_u16x2(w[2] & 0x7fff7fffu, w[3] & 0x7fff7fffu));
-    m = max(m & 0xffffu, m >> 16);
-    const unsigned lane = threadIdx.x & 31u, first = lane & ~3u;
-    unsigned quad = 0xFu << first;
-    if (val > 0) { // vectors of this block that exist: all four except in the array's last block
-        const int left = val - ((int)vec_idx - (int)(lane & 3u)); // vector counts stay below 2^31
-        if (left < 4) quad = ((1u << left) - 1u) << first;
-    }
-    if (quad == (0xFu << first)) {
-        m = max(m, __shfl_xor_sync(quad, m, 1));
-        m = max(m, __shfl_xor_sync(quad, m, 2));
+    const unsigned lane = threadIdx.x & 31u;
+    // The whole warp is here together and every lane's block is whole (any chunk but a ragged first or last one,
+    // any block but the last one of an array whose element count is not a multiple of 32): plain full-warp
+    // exchanges, which cost a fraction of exchanges under a partial mask.
+    bool whole_warp = __activemask() == 0xffffffffu;
+    if (whole_warp && val > 0) whole_warp = __all_sync(0xffffffffu, (int)vec_idx - (int)(lane & 3u) + 4 <= val);
+    if (whole_warp) {
+        m = sa_max_u16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = sa_max_u16x2(m, __shfl_xor_sync(0xffffffffu, m, 2));
     } else {
-        m = sa_partial_quad_max(m, quad, first); // the array's last block only
+        const unsigned first = lane & ~3u;
+        unsigned quad = 0xFu << first;
+        if (val > 0) { // vectors of this block that exist: all four except in the array's last block
+            const int left = val - ((int)vec_idx - (int)(lane & 3u)); // vector counts stay below 2^31
+            if (left < 4) quad = ((1u << left) - 1u) << first;
+        }
+        m = sa_partial_quad_max(m, quad, first);
     }
-    // floor(log2(amax)) is the exponent field; bf16 subnormals have field 0 and get the smallest scale, like zero
-    const int field = (int)(m >> 7);
-    const int scale_byte = field > 8 ? field - 8 : 0;                   // E8M0: shared exponent + 127
-    const float mult = __uint_as_float((unsigned)(254 - scale_byte) << 23); // 2^-(shared exponent): 2^-120 .. 2^127
+    // floor(log2(amax)) is the exponent field of the larger half; bf16 subnormals have field 0 and get the
+    // smallest scale, like zero.  E8M0 scale byte = shared exponent + 127 = max(field, 8) - 8; the multiplier
+    // 2^-(shared exponent) has exponent field 254 - scale byte = 262 - max(field, 8): 2^-120 .. 2^127, a normal float.
+    const int t = max(max((int)((m >> 7) & 0xffu), (int)(m >> 23)), 8);
+    const float mult = __uint_as_float((unsigned)t * 0xFF800000u + (262u << 23)); // (262 - t) << 23 as one multiply-add
     unsigned packed[2];
 #pragma unroll
     for (int i = 0; i < 2; i++) {
-        float2 a, b;
-        a.x = __fmul_rn(__uint_as_float(w[2 * i] << 16), mult);
-        a.y = __fmul_rn(__uint_as_float(w[2 * i] & 0xffff0000u), mult);
-        b.x = __fmul_rn(__uint_as_float(w[2 * i + 1] << 16), mult);
-        b.y = __fmul_rn(__uint_as_float(w[2 * i + 1] & 0xffff0000u), mult);
-        packed[i] = (unsigned)__nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3) |
-                    ((unsigned)__nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3) << 16);
+        const float a0 = __fmul_rn(__uint_as_float(w[2 * i] << 16), mult);
+        const float a1 = __fmul_rn(__uint_as_float(w[2 * i] & 0xffff0000u), mult);
+        const float b0 = __fmul_rn(__uint_as_float(w[2 * i + 1] << 16), mult);
+        const float b1 = __fmul_rn(__uint_as_float(w[2 * i + 1] & 0xffff0000u), mult);
+        // four floats to four E4M3 bytes (round to nearest even, saturating at +-448), first element in the lowest byte
+        asm("{ .reg .b16 lo, hi; cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1; cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3; "
+            "mov.b32 %0, {lo, hi}; }"
+            : "=r"(packed[i]) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
     }
     *(uint2 *)out0 = make_uint2(packed[0], packed[1]);
-    if ((lane & 3u) == 0u) ((unsigned char *)mem)[vec_idx >> 2] = (unsigned char)scale_byte;
+    // all lanes of the quad hold the same scale and store it to the same byte (no branch; one of the four equal
+    // writes lands); a lane of a partial last block stores for the block it belongs to as well
+    ((unsigned char *)mem)[(size_t)vec_idx >> 2] = (unsigned char)(t - 8);
 }
 """

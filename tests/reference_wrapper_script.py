@@ -45,7 +45,7 @@ def main():
 
     # memcpy: a small block (runtime pool) and two large ones (side-aware blocks, one needing 64-bit indexing)
     ok = True
-    for n in (4 * 777, 12 << 20, (2 << 30) + 4096):
+    for n in (4 * 777 * 4, 12 << 20, (2 << 30) + 4096):  # bytes; the first is test.py's (4, 777) fp32 tensor
         src = torch.arange(n // 4, dtype=torch.int32, device="cuda")
         dst = torch.zeros_like(src)
         torch.ops.sideaware.memcpy(dst, src)
