@@ -40,7 +40,15 @@ void sideaware_free_auto(void* ptr, size_t size, int device, sideaware_stream_t 
 /* ---- configuration (sideaware_alloc.cu:724-734) ---------------------------- */
 void sideaware_compression(bool enable);
 void sideaware_alloc_threshold(size_t threshold); /* smaller requests of the *_auto calls go to cudaMallocAsync */
-void sideaware_prealloc_config(int extra_required, int extra_alloc); /* accepted; memory is created on demand here */
+/* In 2 MiB pages (sideaware.cu:1475-1478, top-up rule :1066-1080).  extra_alloc: whenever the mapped set has to
+ * grow, that many pages more than asked for are mapped, as a free run behind the new block.  extra_required: if a
+ * request leaves fewer free pages than this at hand (mapped-and-free or pooled), the next free call maps
+ * extra_alloc more.  Defaults 1 and 10, the reference's.  0 for extra_alloc switches both off. */
+void sideaware_prealloc_config(int extra_required, int extra_alloc);
+/* Maps `bytes` of side-placed memory now, as one free run on `device` (< 0: the current one), so that later
+ * requests up to that size find their pages mapped (about 2 us instead of about 80 us per 2 MiB page).
+ * No counterpart in the reference, whose preallocation (sideaware.cu:934-1034) runs only inside a request. */
+sideaware_status_t sideaware_prealloc(size_t bytes, int device);
 void sideaware_free_mapped_thresholds(size_t start_threshold, size_t end_threshold);
 
 /* ---- queries (sideaware_alloc.cu:736-762) ----------------------------------- */
@@ -87,6 +95,8 @@ typedef struct sideaware_stats_t {
     unsigned long long handles_discarded;      /* handles given back because their pages' sides did not alternate */
     unsigned long long extensions;             /* blocks placed behind the last page of an existing segment */
     unsigned long long hole_refills;           /* blocks mapped into a hole that a trim had left inside a segment */
+    unsigned long long headroom_pages;         /* pages mapped beyond what requests asked for (sideaware_prealloc_config) */
+    unsigned long long top_ups;                /* free calls that mapped extra_alloc pages */
 } sideaware_stats_t;
 #endif
 void sideaware_get_stats(sideaware_stats_t* out);

@@ -21,7 +21,7 @@ class Stats(ctypes.Structure):
         "bytes_mapped_live", "bytes_mapped_cached", "pages_pool_side0", "pages_pool_side1", "pages_created",
         "cross_side_pages", "reuse_hits", "large_allocs", "small_allocs", "trims", "jit_compiles",
         "kernel_launches", "probe_confidence_ppm", "hash_validation_errors", "kernel_wait_timeouts",
-        "handles_created", "handles_discarded", "extensions", "hole_refills")]
+        "handles_created", "handles_discarded", "extensions", "hole_refills", "headroom_pages", "top_ups")]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -45,6 +45,7 @@ SIGNATURES = {
     "sideaware_compression": (None, [c.c_bool]),
     "sideaware_alloc_threshold": (None, [_sz]),
     "sideaware_prealloc_config": (None, [_i, _i]),
+    "sideaware_prealloc": (_i, [_sz, _i]),
     "sideaware_free_mapped_thresholds": (None, [_sz, _sz]),
     "sideaware_write_sass": (None, [c.c_char_p]),
     "sideaware_fill_side_index": (None, [_vp]),

@@ -118,16 +118,14 @@ void SaAllocator::insert_free(uint64_t va, Run run) {
     auto merge = [](Run& into, const Run& other) {
         into.pages += other.pages;
         into.freed_seq = std::max(into.freed_seq, other.freed_seq);
-        if (into.clean) { // the other one's user is the only one to wait for
+        if (into.clean) { // the other one's users are the only ones to wait for
             into.stream = other.stream;
-            into.mixed = other.mixed;
+            into.free_stream = other.free_stream;
             into.clean = other.clean;
-        } else if (!other.clean && (other.mixed || other.stream != into.stream)) {
-            into.mixed = true;
         }
     };
     auto same_user = [](const Run& a, const Run& b) {
-        return a.clean || b.clean || (a.stream == b.stream && !a.mixed && !b.mixed);
+        return a.clean || b.clean || (a.stream == b.stream && a.free_stream == b.free_stream);
     };
     auto next = free_.lower_bound(va);
     if (next != free_.end() && next->second.seg == run.seg && va + run.pages * kSaPageBytes == next->first &&
@@ -153,6 +151,15 @@ void SaAllocator::insert_free(uint64_t va, Run run) {
     cached_bytes_ += run.pages * kSaPageBytes;
 }
 
+// Work queued by the previous users of a run (the stream it was handed out on and, if the caller moved the block,
+// the stream it was freed on) must be done before a different stream touches the pages: ordered on the device
+// through an event, the host does not wait (the reference blocks the host, sideaware.cu:1209-1214).
+void SaAllocator::wait_for_users(const Run& run, void* stream) {
+    if (run.clean) return;
+    if (run.stream != stream) be_->order_after(run.stream, stream);
+    if (run.free_stream != run.stream && run.free_stream != stream) be_->order_after(run.free_stream, stream);
+}
+
 // Best fit: the shortest free run that can hold `pages` pages starting on side `phase`
 // (a run that starts on the other side needs one page more; that page stays free).  Among the
 // shortest few, one last used on the asking stream is preferred: it needs no waiting.
@@ -167,7 +174,7 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
         auto cand = free_.find(it->second);
         ++looked;
         if (pick == free_.end()) pick = cand;
-        if (cand->second.clean || (!cand->second.mixed && cand->second.stream == stream)) { pick = cand; break; }
+        if (cand->second.clean || (cand->second.stream == stream && cand->second.free_stream == stream)) { pick = cand; break; }
     }
     if (pick == free_.end()) return 0;
     const uint64_t run_va = pick->first;
@@ -186,10 +193,7 @@ uint64_t SaAllocator::take_from_free(size_t pages, int phase, bool compressed, v
         rest.pages = tail;
         insert_free(base + pages * kSaPageBytes, rest);
     }
-    // work queued by the previous user(s) of these pages must be done before a different stream touches them
-    if (run.clean) {}
-    else if (run.mixed) be_->device_sync();
-    else if (run.stream != stream) be_->order_after(run.stream, stream);
+    wait_for_users(run, stream);
     Block b;
     b.pages = pages;
     b.seg = run.seg;
@@ -516,29 +520,39 @@ bool SaAllocator::map_slots(Segment* seg, size_t lo, size_t hi, void* stream) {
 static size_t segment_slack(size_t pages) { return std::max<size_t>(3 * pages, 4096); }
 
 // Maps a new segment of `pages` pages whose first page is on side `phase` and hands all of it out
-// as one block.
-uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg) {
-    (void)cfg;
+// as one block; `headroom` more pages are mapped behind it as a free run (dropped if memory is short).
+uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* stream, size_t headroom) {
     std::unique_ptr<Segment> seg(new Segment());
     seg->compressed = compressed;
     // one spare page of address space lets us pick the phase of bit 21
-    seg->capacity = pages + segment_slack(pages);
+    seg->capacity = pages + headroom + segment_slack(pages);
     seg->reserved_bytes = (seg->capacity + 1) * kSaPageBytes;
     if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) {
         // address space is short: no room to extend, then
+        headroom = 0;
         seg->capacity = pages;
         seg->reserved_bytes = (pages + 1) * kSaPageBytes;
         if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
     }
     seg->base = seg->reserved;
     if (side_bit(seg->base) != phase) seg->base += kSaPageBytes;
-    seg->pages.assign(pages, Slot{});
-    seg->num_pages = pages;
-    if (!map_slots(seg.get(), 0, pages, stream)) {
-        be_->free_va(seg->reserved, seg->reserved_bytes);
-        return 0;
+    seg->pages.assign(pages + headroom, Slot{});
+    seg->num_pages = pages + headroom;
+    if (!map_slots(seg.get(), 0, pages + headroom, stream)) {
+        // memory may be too short for the headroom: the request alone, then
+        bool ok = false;
+        if (headroom) {
+            headroom = 0;
+            seg->pages.assign(pages, Slot{});
+            seg->num_pages = pages;
+            ok = map_slots(seg.get(), 0, pages, stream);
+        }
+        if (!ok) {
+            be_->free_va(seg->reserved, seg->reserved_bytes);
+            return 0;
+        }
     }
-    seg->mapped_pages = pages;
+    seg->mapped_pages = pages + headroom;
     Block b;
     b.pages = pages;
     b.seg = seg.get();
@@ -546,6 +560,16 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
     const uint64_t base = seg->base;
     live_.emplace(base, b);
     live_bytes_ += pages * kSaPageBytes;
+    if (headroom) { // mapped and measured, never used: a free run right behind the block
+        Run spare;
+        spare.pages = headroom;
+        spare.seg = seg.get();
+        spare.freed_seq = ++seq_;
+        spare.stream = spare.free_stream = stream;
+        spare.clean = true;
+        insert_free(base + pages * kSaPageBytes, spare);
+        st_.headroom_pages += headroom;
+    }
     segments_.push_back(std::move(seg));
     return base;
 }
@@ -556,7 +580,7 @@ uint64_t SaAllocator::grow(size_t pages, int phase, bool compressed, void* strea
 // taken.  Otherwise the block starts right behind the segment's last block (one page further if
 // that slot is on the wrong side; the skipped page is mapped too and becomes a free run, so that
 // the neighbours can still merge across it).
-uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* stream) {
+uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* stream, size_t headroom) {
     Segment* best = nullptr;
     uint64_t best_va = 0;
     size_t best_have = 0, best_room = 0, best_lead = 0;
@@ -603,14 +627,34 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
     const uint64_t end = best->base + old_pages * kSaPageBytes;
     const size_t lead = best_have ? 0 : (side_bit(end) == phase ? 0 : 1);
     const size_t extra = lead + (pages - best_have);
-    best->pages.resize(old_pages + extra, Slot{});
-    if (!map_slots(best, old_pages, old_pages + extra, stream)) {
-        best->pages.resize(old_pages);
-        if (best_have) insert_free(best_va, run);
-        return 0;
+    // pages beyond the request, as far as the segment has room: they stay behind the block as a free run
+    headroom = std::min(headroom, best->capacity - (old_pages + extra));
+    best->pages.resize(old_pages + extra + headroom, Slot{});
+    if (!map_slots(best, old_pages, old_pages + extra + headroom, stream)) {
+        bool ok = false;
+        if (headroom) { // memory may be too short for the headroom: the request alone, then
+            headroom = 0;
+            best->pages.resize(old_pages + extra);
+            ok = map_slots(best, old_pages, old_pages + extra, stream);
+        }
+        if (!ok) {
+            best->pages.resize(old_pages);
+            if (best_have) insert_free(best_va, run);
+            return 0;
+        }
     }
-    best->num_pages = old_pages + extra;
-    best->mapped_pages += extra;
+    best->num_pages = old_pages + extra + headroom;
+    best->mapped_pages += extra + headroom;
+    if (headroom) {
+        Run spare;
+        spare.pages = headroom;
+        spare.seg = best;
+        spare.freed_seq = ++seq_;
+        spare.stream = spare.free_stream = stream;
+        spare.clean = true; // never used
+        insert_free(best->base + (old_pages + extra) * kSaPageBytes, spare);
+        st_.headroom_pages += headroom;
+    }
     uint64_t base;
     if (best_have) {
         if (skip) {
@@ -618,10 +662,7 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
             head.pages = 1;
             insert_free(best_va, head);
         }
-        // work queued by the previous user(s) of the run must be done before a different stream touches it
-        if (run.clean) {}
-        else if (run.mixed) be_->device_sync();
-        else if (run.stream != stream) be_->order_after(run.stream, stream);
+        wait_for_users(run, stream);
         base = best_va + skip * kSaPageBytes;
     } else {
         if (lead) {
@@ -629,7 +670,7 @@ uint64_t SaAllocator::extend(size_t pages, int phase, bool compressed, void* str
             gap.pages = 1;
             gap.seg = best;
             gap.freed_seq = ++seq_;
-            gap.stream = stream;
+            gap.stream = gap.free_stream = stream;
             gap.clean = true; // never used
             insert_free(end, gap);
         }
@@ -757,7 +798,6 @@ void SaAllocator::merge_all_free_runs() {
     all.reserve(free_.size());
     for (auto& kv : free_) {
         kv.second.clean = true;
-        kv.second.mixed = false;
         all.push_back(kv.first);
     }
     for (uint64_t va : all) {
@@ -826,27 +866,43 @@ int SaAllocator::choose_phase(size_t bytes, size_t pages, bool compressed) {
     return phase;
 }
 
+// free pages a request could be served from without creating physical memory: mapped-and-free plus pooled
+size_t SaAllocator::pages_at_hand(bool compressed) const {
+    return cached_bytes_ / kSaPageBytes + pooled_pages(compressed, 0) + pooled_pages(compressed, 1);
+}
+
 uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg) {
     std::lock_guard<std::mutex> lock(mu_);
+    return malloc_locked(size, stream, cfg);
+}
+
+uint64_t SaAllocator::malloc_locked(size_t size, void* stream, const SaAllocConfig& cfg) {
     const size_t bytes = round_to_pages(size);
     const size_t pages = bytes / kSaPageBytes;
     const bool compressed = cfg.compression && comp_ok_;
     if (capacity_ && bytes > capacity_) return 0; // can never fit: do not drain the device trying
     const int phase = choose_phase(bytes, pages, compressed);
+    auto served = [&](uint64_t p) {
+        live_[p].requested = size;
+        live_of_size_[bytes]++;
+        st_.large_allocs++;
+        // too little left at hand for the next request: the next free() maps some more (top_up)
+        want_top_up_ = cfg.extra_required > 0 && cfg.extra_alloc > 0 && pages_at_hand(compressed) < (size_t)cfg.extra_required;
+        return p;
+    };
 
     // 1) a free run of still-mapped pages (no driver call at all)
     uint64_t p = take_from_free(pages, phase, compressed, stream);
     if (p) {
-        live_[p].requested = size;
-        live_of_size_[bytes]++;
         st_.reuse_hits++;
-        st_.large_allocs++;
-        return p;
+        return served(p);
     }
     // 2..4) the ladder of sideaware.cu:1233-1252: unmap free memory above the threshold, unmap
     // all of it, give all pooled pages back to the driver; try to grow the mapped set after each.
     // Growing: into a hole an earlier trim left, else behind the last page of a segment (using the free run
-    // there, if any), else a new segment.
+    // there, if any), else a new segment.  While memory is not short the mapped set grows by extra_alloc pages
+    // more than asked for (the reference creates that many spare pages whenever it has to create any,
+    // sideaware.cu:1074-1076): the fixed cost of a round of driver calls and measurements is paid less often.
     for (int step = 0; step < 3; ++step) {
         if (step == 0) trim_locked(cfg.trim_start, cfg.trim_end);
         else if (step == 1) trim_locked(0, 0);
@@ -855,19 +911,99 @@ uint64_t SaAllocator::malloc(size_t size, void* stream, const SaAllocConfig& cfg
             release_pools();
             be_->device_sync();
         }
+        const size_t headroom = (step == 0 && cfg.extra_alloc > 0) ? (size_t)cfg.extra_alloc : 0;
         p = refill(pages, phase, compressed, stream);
-        if (!p && step == 0) p = extend(pages, phase, compressed, stream);
-        if (!p) p = grow(pages, phase, compressed, stream, cfg);
-        if (p) {
-            live_[p].requested = size;
-            live_of_size_[bytes]++;
-            st_.large_allocs++;
-            return p;
-        }
+        if (!p && step == 0) p = extend(pages, phase, compressed, stream, headroom);
+        if (!p) p = grow(pages, phase, compressed, stream, headroom);
+        if (p) return served(p);
     }
     // nothing worked: do not sit on the pages gathered while trying
     release_pools();
     return 0;
+}
+
+// Maps `pages` more pages as a free run: behind the last page of the segment with the most pages that has room
+// (blocks cluster there), else as a segment of its own.  Returns the pages mapped; 0 leaves everything as it was.
+size_t SaAllocator::add_headroom(size_t pages, bool compressed, void* stream) {
+    if (pages == 0) return 0;
+    Segment* best = nullptr;
+    for (auto& sp : segments_) {
+        Segment* seg = sp.get();
+        if (seg->compressed != compressed || seg->num_pages + pages > seg->capacity) continue;
+        if (!best || seg->num_pages > best->num_pages) best = seg;
+    }
+    Run spare;
+    spare.pages = pages;
+    spare.freed_seq = ++seq_;
+    spare.stream = spare.free_stream = stream;
+    spare.clean = true; // never used
+    if (best) {
+        const size_t old_pages = best->num_pages;
+        best->pages.resize(old_pages + pages, Slot{});
+        if (!map_slots(best, old_pages, old_pages + pages, stream)) {
+            best->pages.resize(old_pages);
+            return 0;
+        }
+        best->num_pages = old_pages + pages;
+        best->mapped_pages += pages;
+        spare.seg = best;
+        insert_free(best->base + old_pages * kSaPageBytes, spare);
+    } else {
+        std::unique_ptr<Segment> seg(new Segment());
+        seg->compressed = compressed;
+        seg->capacity = pages + segment_slack(pages);
+        seg->reserved_bytes = (seg->capacity + 1) * kSaPageBytes;
+        if (be_->reserve_va(&seg->reserved, seg->reserved_bytes)) return 0;
+        seg->base = seg->reserved;
+        seg->pages.assign(pages, Slot{});
+        seg->num_pages = pages;
+        if (!map_slots(seg.get(), 0, pages, stream)) {
+            be_->free_va(seg->reserved, seg->reserved_bytes);
+            return 0;
+        }
+        seg->mapped_pages = pages;
+        spare.seg = seg.get();
+        insert_free(seg->base, spare);
+        segments_.push_back(std::move(seg));
+    }
+    st_.headroom_pages += pages;
+    return pages;
+}
+
+size_t SaAllocator::top_up(void* stream, const SaAllocConfig& cfg) {
+    std::lock_guard<std::mutex> lock(mu_);
+    if (!want_top_up_) return 0;
+    want_top_up_ = false;
+    const bool compressed = cfg.compression && comp_ok_;
+    if (cfg.extra_alloc <= 0 || pages_at_hand(compressed) >= (size_t)std::max(cfg.extra_required, 0)) return 0;
+    const size_t got = add_headroom((size_t)cfg.extra_alloc, compressed, stream);
+    if (got) st_.top_ups++;
+    return got;
+}
+
+bool SaAllocator::prealloc(size_t size, const SaAllocConfig& cfg) {
+    std::lock_guard<std::mutex> lock(mu_);
+    // a block of that size, given straight back: what stays is a free run nobody has used
+    SaAllocConfig plain = cfg;
+    plain.extra_alloc = 0;
+    const uint64_t p = malloc_locked(size, nullptr, plain);
+    if (!p) return false;
+    auto it = live_.find(p);
+    Block b = it->second;
+    live_.erase(it);
+    live_bytes_ -= b.pages * kSaPageBytes;
+    auto lc = live_of_size_.find(b.pages * kSaPageBytes);
+    if (lc != live_of_size_.end() && lc->second > 0) lc->second--;
+    st_.large_allocs--;
+    Run run;
+    run.pages = b.pages;
+    run.seg = b.seg;
+    run.freed_seq = ++seq_;
+    run.stream = run.free_stream = nullptr;
+    run.clean = false; // the pages may have come from a run whose last user is still at work: keep its ordering
+    insert_free(p, run);
+    want_top_up_ = false;
+    return true;
 }
 
 bool SaAllocator::free(uint64_t ptr, void* stream) {
@@ -879,12 +1015,14 @@ bool SaAllocator::free(uint64_t ptr, void* stream) {
     live_bytes_ -= b.pages * kSaPageBytes;
     auto lc = live_of_size_.find(b.pages * kSaPageBytes);
     if (lc != live_of_size_.end() && lc->second > 0) lc->second--;
-    (void)stream; // the run remembers the stream the block was handed out on (sideaware.cu:1209-1214)
+    // the run remembers the stream the block was handed out on (sideaware.cu:1209-1214) and the one it is freed on:
+    // whoever gets these pages next is ordered behind both
     Run run;
     run.pages = b.pages;
     run.seg = b.seg;
     run.freed_seq = ++seq_;
     run.stream = b.stream;
+    run.free_stream = stream;
     insert_free(ptr, run);
     return true;
 }

@@ -78,8 +78,11 @@ struct SaBackend {
 struct SaAllocConfig {
     size_t trim_start = 16ull << 30; // when the mapped set must grow and more than this is free-but-mapped, unmap
     size_t trim_end = 2ull << 30;    // ... least recently freed runs down to this
-    int extra_required = 1;          // accepted for compatibility with the reference's setter; pages are
-    int extra_alloc = 10;            // created on demand, straight into the segment that needs them
+    // sideaware_prealloc_config (sideaware.cu:1475-1478; the reference's top-up rule is :1066-1080), in 2 MiB pages:
+    int extra_required = 1;          // after a request has been served, at least this many free pages should still be
+                                     // at hand (mapped-and-free, or pooled); if not, the next free() tops them up
+    int extra_alloc = 10;            // pages mapped beyond the request whenever the mapped set has to grow, and per top-up:
+                                     // they lie behind the block as a free run, so the next requests find memory mapped
     bool compression = false;
 };
 
@@ -89,6 +92,8 @@ struct SaAllocStats {
     uint64_t segments = 0, free_runs = 0;
     uint64_t handles_created = 0;   // cuMemCreate calls (pages_created counts their pages)
     uint64_t handles_discarded = 0; // created, measured, found unusable (pages do not alternate), given back
+    uint64_t headroom_pages = 0;    // pages mapped beyond what a request asked for (growth headroom and top-ups)
+    uint64_t top_ups = 0;           // free-time top-ups that mapped something
     uint64_t extensions = 0;        // blocks made of a segment's last free run plus newly mapped pages
     uint64_t hole_refills = 0;      // blocks mapped into a hole that a trim had left inside a segment
 };
@@ -105,6 +110,13 @@ public:
     // true if `ptr` was a live block of this allocator (its pages are now free, still mapped)
     bool free(uint64_t ptr, void* stream);
     bool owns(uint64_t ptr);
+    // Free-time upkeep: if the last request left fewer than cfg.extra_required free pages at hand, maps
+    // cfg.extra_alloc more as a free run behind the largest segment.  Returns the pages it mapped (0 = nothing to do
+    // or the driver refused; a refusal leaves everything as it was).
+    size_t top_up(void* stream, const SaAllocConfig& cfg);
+    // Makes sure a free, mapped, side-placed run of at least `size` bytes exists now (growing the mapped set if
+    // need be), so that later requests up to that size are served without a driver call.  False if it cannot.
+    bool prealloc(size_t size, const SaAllocConfig& cfg);
     // If more than `start` bytes are free-but-mapped and could be unmapped: unmap free runs, least
     // recently freed first, until at most `end` such bytes are left.
     void trim(size_t start, size_t end);
@@ -130,9 +142,9 @@ private:
         size_t pages = 0;
         Segment* seg = nullptr;
         uint64_t freed_seq = 0;
-        void* stream = nullptr; // stream of the last user(s); mixed = several
-        bool mixed = false;
-        bool clean = false;     // nobody's work is pending on these pages (never used, or the device was synchronised since)
+        void* stream = nullptr;      // stream the block was handed out on
+        void* free_stream = nullptr; // stream it was freed on (the same one, unless the caller moved the block between streams)
+        bool clean = false;          // nobody's work is pending on these pages (never used, or the device was synchronised since)
     };
     struct Block {
         size_t pages = 0, requested = 0;
@@ -141,8 +153,12 @@ private:
     };
 
     uint64_t take_from_free(size_t pages, int phase, bool compressed, void* stream);
-    uint64_t grow(size_t pages, int phase, bool compressed, void* stream, const SaAllocConfig& cfg);
-    uint64_t extend(size_t pages, int phase, bool compressed, void* stream);
+    uint64_t grow(size_t pages, int phase, bool compressed, void* stream, size_t headroom);
+    uint64_t extend(size_t pages, int phase, bool compressed, void* stream, size_t headroom);
+    size_t add_headroom(size_t pages, bool compressed, void* stream);
+    void wait_for_users(const Run& run, void* stream);
+    uint64_t malloc_locked(size_t size, void* stream, const SaAllocConfig& cfg);
+    size_t pages_at_hand(bool compressed) const;
     uint64_t refill(size_t pages, int phase, bool compressed, void* stream);
     bool map_slots(Segment* seg, size_t lo, size_t hi, void* stream);
     void insert_free(uint64_t va, Run run);
@@ -185,5 +201,6 @@ private:
     size_t cached_bytes_ = 0, live_bytes_ = 0;
     uint64_t seq_ = 0;
     bool warned_cross_ = false;
+    bool want_top_up_ = false; // the last request left too little at hand: the next free() tops up
     SaAllocStats st_;
 };

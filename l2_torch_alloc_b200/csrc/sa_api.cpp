@@ -38,7 +38,16 @@ void* malloc_large(SaDevice* dev, size_t size, cudaStream_t stream) {
 // Unknown pointers are handed to the runtime's pool, as the reference does (sideaware.cu:1258-1261).
 cudaError_t free_large(SaDevice* dev, void* ptr, cudaStream_t stream) {
     if (!ptr) return cudaSuccess;
-    if (dev->alloc->free((uint64_t)ptr, (void*)stream)) return cudaSuccess;
+    if (dev->alloc->free((uint64_t)ptr, (void*)stream)) {
+        // free-time upkeep (sideaware_prealloc_config): nothing but a flag test unless the last request ran the
+        // free memory at hand down below extra_required
+        const SaAllocConfig cfg = alloc_config_now();
+        if (cfg.extra_alloc > 0 && cfg.extra_required > 0) {
+            SaScopedDevice guard(dev->id);
+            dev->alloc->top_up((void*)stream, cfg);
+        }
+        return cudaSuccess;
+    }
     SaScopedDevice guard(dev->id);
     return cudaFreeAsync(ptr, stream);
 }
@@ -101,6 +110,18 @@ SA_API sideaware_status_t sideaware_free(void* ptr) {
         return e;
     }
     return free_large(dev, ptr, nullptr);
+}
+
+SA_API sideaware_status_t sideaware_prealloc(size_t bytes, int device) {
+    if (bytes == 0) return cudaSuccess;
+    SaDevice* dev = sa_device(device);
+    if (!dev) return cudaErrorInitializationError;
+    SaScopedDevice guard(dev->id);
+    if (!dev->alloc->prealloc(bytes, alloc_config_now())) {
+        sa_set_error("device %d: out of memory mapping %zu bytes ahead of need", dev->id, bytes);
+        return cudaErrorMemoryAllocation;
+    }
+    return cudaSuccess;
 }
 
 SA_API size_t sideaware_release_unused(void) {
@@ -491,6 +512,8 @@ SA_API void sideaware_get_stats(sideaware_stats_t* out) {
     out->handles_discarded = st.handles_discarded;
     out->extensions = st.extensions;
     out->hole_refills = st.hole_refills;
+    out->headroom_pages = st.headroom_pages;
+    out->top_ups = st.top_ups;
     out->jit_compiles = dev->jit_compiles.load();
     out->kernel_launches = dev->launches.load();
     out->probe_confidence_ppm = (unsigned long long)(dev->topo.confidence > 0 ? dev->topo.confidence * 1e6 : 0);

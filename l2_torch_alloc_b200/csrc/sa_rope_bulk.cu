@@ -112,7 +112,7 @@ sa_rope_bulk_kernel(const __grid_constant__ SaSched s, const __grid_constant__ S
     // load is issued and wait in registers, in the order of the ring, until the chunk is rotated: their latency
     // is hidden behind the data's.  Slot 0 belongs to the oldest chunk in flight.
     constexpr int kQueue = (int)kLoadsInFlight + 1;
-    RopeTab<BF16> tabs[kQueue][2];
+    RopeTab<BF16> tabs[kQueue][2] = {};
 
     // wait for the oldest chunk in flight, rotate it in shared memory, send it back
     auto retire = [&]() {

@@ -356,6 +356,7 @@ int FakeDriver::default_model = 0;
 
 static void test_alloc() {
     SaAllocConfig cfg;
+    cfg.extra_alloc = 0; // exact page counts below: no headroom unless a case asks for it
     {   // basic: alignment, side placement, phase rule, reuse
         FakeDriver d;
         SaAllocator a(&d, false);
@@ -416,6 +417,120 @@ static void test_alloc() {
                 a.release_unused();
                 CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
             }
+    }
+    {   // growth headroom and free-time top-up (sideaware_prealloc_config)
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        SaAllocConfig c2 = cfg;
+        c2.extra_required = 4;
+        c2.extra_alloc = 12;
+        uint64_t p1 = a.malloc(32u << 20, (void*)1, c2); // 16 pages asked for, 12 more mapped behind them
+        CHECK(p1 != 0 && d.wrong_side_pages(p1, 32u << 20) == 0);
+        SaAllocStats st = a.stats();
+        CHECK(st.headroom_pages == 12 && st.bytes_cached == 12 * kSaPageBytes && st.bytes_live == (32u << 20));
+        CHECK(d.wrong_side_pages(p1 + (32u << 20), 12 * kSaPageBytes) == 0); // the headroom is side-placed too
+        const int creates = d.creates;
+        uint64_t p2 = a.malloc(16u << 20, (void*)1, c2); // served from the headroom: no driver call
+        CHECK(p2 == p1 + (32u << 20) && d.creates == creates && d.stream_syncs == 0);
+        uint64_t p3 = a.malloc(8u << 20, (void*)2, c2);  // another stream: the headroom was never used, nothing to wait for
+        CHECK(p3 != 0 && d.creates == creates && d.stream_syncs == 0);
+        // 0 pages left at hand < extra_required: the next free tops up by extra_alloc
+        st = a.stats();
+        CHECK(st.bytes_cached == 0);
+        const bool short_of_pages = st.pages_pool[0] + st.pages_pool[1] < 4; // pooled pages count as "at hand" too
+        CHECK(a.top_up((void*)1, c2) == (short_of_pages ? 12u : 0u));
+        CHECK(a.top_up((void*)1, c2) == 0); // once per shortage
+        st = a.stats();
+        if (short_of_pages) CHECK(st.top_ups == 1 && st.headroom_pages == 24 && st.bytes_cached == 12 * kSaPageBytes);
+        size_t accounted = st.pages_pool[0] + st.pages_pool[1] + (st.bytes_live + st.bytes_cached) / kSaPageBytes;
+        CHECK(accounted == d.live_pages());
+        // with plenty at hand nothing is topped up
+        uint64_t p4 = a.malloc(2u << 20, (void*)1, c2);
+        CHECK(p4 != 0 && a.top_up((void*)1, c2) == 0);
+        // switched off: growth maps exactly what is asked for
+        SaAllocConfig off = cfg;
+        off.extra_alloc = 0;
+        const size_t mapped = d.mappings.size();
+        uint64_t p5 = a.malloc(64u << 20, (void*)1, off);
+        CHECK(p5 != 0 && d.mappings.size() <= mapped + 32 + 1); // at most one page skipped for the side
+        for (uint64_t p : {p1, p2, p4, p5}) a.free(p, (void*)1);
+        a.free(p3, (void*)2);
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
+    }
+    {   // a top-up or a headroom that the driver refuses half-way leaves everything as it was
+        for (int kind = 0; kind < 5; ++kind)
+            for (int k = 0; k < 12; ++k) {
+                FakeDriver d;
+                SaAllocator a(&d, false);
+                SaAllocConfig c2 = cfg;
+                c2.extra_required = 64;
+                c2.extra_alloc = 24;
+                uint64_t p1 = a.malloc(8u << 20, nullptr, c2);
+                CHECK(p1 != 0);
+                SaAllocStats before = a.stats();
+                const size_t mapped_before = d.mappings.size();
+                int* knob = kind == 0 ? &d.fail_create_after : kind == 1 ? &d.fail_map_after : kind == 2 ? &d.fail_reserve_after
+                          : kind == 3 ? &d.fail_access_after : &d.fail_probe_after;
+                *knob = k;
+                const size_t got = a.top_up(nullptr, c2);
+                SaAllocStats after = a.stats();
+                CHECK(got == 0 || got == 24);
+                if (got == 0) {
+                    CHECK(after.bytes_cached == before.bytes_cached && d.mappings.size() == mapped_before);
+                } else {
+                    CHECK(after.bytes_cached == before.bytes_cached + 24 * kSaPageBytes);
+                }
+                CHECK(after.bytes_live == before.bytes_live);
+                size_t accounted = after.pages_pool[0] + after.pages_pool[1] + (after.bytes_live + after.bytes_cached) / kSaPageBytes;
+                CHECK(accounted == d.live_pages());
+                CHECK(d.mappings.size() == (after.bytes_live + after.bytes_cached) / kSaPageBytes);
+                *knob = -1;
+                // a request with headroom whose headroom part fails still gets its block
+                *knob = k + 2;
+                uint64_t p2 = a.malloc(48u << 20, nullptr, c2);
+                *knob = -1;
+                if (p2) CHECK(d.wrong_side_pages(p2, 48u << 20) == 0);
+                after = a.stats();
+                accounted = after.pages_pool[0] + after.pages_pool[1] + (after.bytes_live + after.bytes_cached) / kSaPageBytes;
+                CHECK(accounted == d.live_pages());
+                if (p2) a.free(p2, nullptr);
+                a.free(p1, nullptr);
+                a.release_unused();
+                CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
+            }
+    }
+    {   // mapping ahead of need: sideaware_prealloc
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        CHECK(a.prealloc(256u << 20, cfg));
+        SaAllocStats st = a.stats();
+        CHECK(st.bytes_live == 0 && st.bytes_cached >= (256u << 20) && st.large_allocs == 0);
+        const int creates = d.creates;
+        uint64_t p = a.malloc(200u << 20, (void*)3, cfg);
+        CHECK(p != 0 && d.creates == creates && d.wrong_side_pages(p, 200u << 20) == 0); // found mapped
+        CHECK(a.prealloc(16u << 20, cfg) && d.creates == creates);                    // already there: nothing to do
+        a.free(p, (void*)3);
+        a.release_unused();
+        CHECK(d.mappings.empty() && d.handles.empty() && d.reservations.empty());
+    }
+    {   // a block handed out on one stream and freed on another is ordered behind both when it is reused
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        SaAllocConfig off = cfg;
+        off.extra_alloc = 0;
+        uint64_t p = a.malloc(16u << 20, (void*)1, off);
+        a.free(p, (void*)2);
+        uint64_t q = a.malloc(16u << 20, (void*)1, off); // back on the stream it came from: still has to wait for stream 2
+        CHECK(q == p && d.stream_syncs == 1);
+        a.free(q, (void*)1);
+        q = a.malloc(16u << 20, (void*)3, off);
+        CHECK(q == p && d.stream_syncs == 2);             // only stream 1 used it this time
+        a.free(q, (void*)4);
+        q = a.malloc(16u << 20, (void*)5, off);
+        CHECK(q == p && d.stream_syncs == 4);             // streams 3 and 4
+        a.free(q, (void*)5);
+        a.release_unused();
     }
     {   // out of memory: the ladder unmaps the cache, then gives up cleanly
         FakeDriver d;
@@ -717,6 +832,7 @@ static void test_alloc() {
 // How many driver calls growth needs under each model of the physical layout.
 static void test_alloc_chunks() {
     SaAllocConfig cfg;
+    cfg.extra_alloc = 0; // exact handle counts below
     const size_t pages = 512; // 1 GiB
     for (int model = 0; model < 3; ++model) {
         FakeDriver d;

@@ -180,6 +180,54 @@ def test_concurrent_malloc_free(sa):
     assert sa.stats()["bytes_mapped_live"] == 0
 
 
+def test_mapping_ahead_of_need(sa):
+    """sideaware_prealloc maps side-placed memory before it is asked for; sideaware_prealloc_config makes growth
+    map a few pages more than asked for and lets free calls top the free memory up (sideaware.cu:1066-1080, :1475-1478)."""
+    import time
+    sa.lib.sideaware_release_unused()
+    GiB = 1 << 30
+    before = sa.stats()
+    t0 = time.perf_counter()
+    assert sa.lib.sideaware_prealloc(GiB, 0) == 0, sa.last_error()
+    t_map = time.perf_counter() - t0
+    st = sa.stats()
+    assert st["bytes_mapped_cached"] - before["bytes_mapped_cached"] >= GiB and st["bytes_mapped_live"] == before["bytes_mapped_live"]
+    t0 = time.perf_counter()
+    p = sa.malloc(GiB)
+    t_first_touch = time.perf_counter() - t0
+    print(f"mapping 1 GiB ahead of need: {t_map * 1e3:.1f} ms; the 1 GiB request after it: {t_first_touch * 1e6:.1f} us")
+    assert t_first_touch < 5e-3, "a request that finds its pages mapped makes no driver call"
+    assert sa.stats()["pages_created"] == st["pages_created"]
+    assert sa.verify_chunk_sides(p, GiB, 512, 7) <= 5
+    sa.free(p)
+    sa.lib.sideaware_release_unused()
+
+    # growth headroom: 64 pages beyond each request that has to grow the mapped set
+    sa.lib.sideaware_prealloc_config(8, 64)
+    try:
+        st0 = sa.stats()
+        a = sa.malloc(64 * MiB)
+        st1 = sa.stats()
+        assert st1["headroom_pages"] - st0["headroom_pages"] == 64
+        assert st1["bytes_mapped_cached"] >= 128 * MiB
+        created = st1["pages_created"]
+        b = sa.malloc(100 * MiB)  # lies in the headroom: nothing is created
+        assert sa.stats()["pages_created"] == created and b == a + 64 * MiB
+        assert sa.verify_chunk_sides(b, 100 * MiB, 256, 3) <= 3
+        c = sa.malloc(24 * MiB)   # 12 of the 14 pages that are left
+        d = sa.malloc(4 * MiB)    # the last two: nothing at hand any more, fewer than extra_required
+        assert sa.stats()["pages_created"] == created
+        tops = sa.stats()["top_ups"]
+        sa.free(d)                # 2 pages at hand after this free: the call maps extra_alloc pages more
+        st2 = sa.stats()
+        assert st2["top_ups"] == tops + 1 and st2["headroom_pages"] - st1["headroom_pages"] == 64
+        for p in (a, b, c):
+            sa.free(p)
+    finally:
+        sa.lib.sideaware_prealloc_config(1, 10)
+        sa.lib.sideaware_release_unused()
+
+
 def test_compressible_memory_option(sa):
     """sideaware_compression(true): pages are created compressible where the device supports it
     (sideaware.cu:817-834, :940); kept apart from plain pages; data round-trips unchanged."""
