@@ -148,8 +148,8 @@ struct SaJitArrays {
     const sa_pack<i3>* pi3;
 };
 
-// One 4 KiB chunk.  Which of its 256 vectors exist (all of them, except in the array's first and last chunk)
-// is worked out once per chunk as a chunk-local range, so the per-vector test is two 32-bit comparisons.
+// One 4 KiB chunk.  `whole` (every vector of the chunk exists: all chunks but the array's first and last) is the
+// same for the whole warp and short-cuts the per-vector range test; measured faster than a chunk-local range test.
 __device__ __forceinline__ void sa_process_chunk(const SaSched& s, const SaJitArgs& a, const SaJitArrays& p,
                                                  sa_u64 first_vec, sa_u32 lane) {
     sa_pack<o0>* const po0 = p.po0;
@@ -161,8 +161,7 @@ __device__ __forceinline__ void sa_process_chunk(const SaSched& s, const SaJitAr
     const sa_pack<i2>* const pi2 = p.pi2;
     const sa_pack<i3>* const pi3 = p.pi3;
     const size_type v0 = (size_type)(first_vec - s.lead) + (size_type)lane; // may be "negative" in the first chunk
-    const sa_u32 lo = first_vec >= s.lead ? 0u : (sa_u32)(s.lead - first_vec);
-    const sa_u32 hi = first_vec + SA_CHUNK_VECS <= s.end ? SA_CHUNK_VECS : (sa_u32)(s.end - first_vec);
+    const bool whole = first_vec >= s.lead && first_vec + SA_CHUNK_VECS <= s.end;
 #pragma unroll 1
     for (int b = 0; b < SA_VEC_PER_LANE / sa_batch; ++b) {
         bool live[sa_batch];
@@ -173,8 +172,8 @@ __device__ __forceinline__ void sa_process_chunk(const SaSched& s, const SaJitAr
 #pragma unroll
         for (int j = 0; j < sa_batch; ++j) {
             const size_type vidx = v0 + (size_type)((b * sa_batch + j) * 32);
-            const sa_u32 in_chunk = (sa_u32)((b * sa_batch + j) * 32) + lane;
-            live[j] = in_chunk >= lo && in_chunk < hi;
+            live[j] = whole || (first_vec + (sa_u64)((b * sa_batch + j) * 32) + lane >= s.lead &&
+                                first_vec + (sa_u64)((b * sa_batch + j) * 32) + lane < s.end);
             if (live[j]) {
                 size_type x0 = 0, x1 = 0, x2 = 0, x3 = 0;
                 live[j] = !indexing(vidx, vec_size, x0, x1, x2, x3, a.mem, a.val);
