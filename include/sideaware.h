@@ -147,7 +147,10 @@ sideaware_status_t sideaware_silu_mul_bf16(void* out, const void* a, const void*
 
 /* Compiles a functor header with NVRTC for sm_100a without loading it, so headers
  * can be checked on a machine without a GPU.  wide != 0 selects the 64-bit index
- * variant.  Returns 0 on success; the compiler log is copied to log_out. */
+ * variant.  Returns 0 on success; the compiler log is copied to log_out.  A header that
+ * uses threadIdx.y, blockDim.y or a block-wide barrier gets a warning line in log_out even
+ * when it compiles: blocks are one-dimensional here and a warp, not a 256-thread group, owns
+ * a chunk (the reference launches (256, groups) blocks, sideaware.cu:1407). */
 int sideaware_compile_check(const char* header, int wide, char* log_out, size_t log_capacity);
 
 /* Kernel placement policy for all launchers: 0 = side-aware (default),

@@ -130,7 +130,13 @@ class SideAware:
             header_code = header_code.encode()
         buf = ctypes.create_string_buffer(1 << 16)
         rc = self.lib.sideaware_compile_check(header_code, 1 if wide else 0, buf, len(buf))
-        return "" if rc == 0 else (buf.value.decode() or "compile failed")
+        log = buf.value.decode()
+        if rc == 0:
+            if log:  # compiles, but uses something that does not carry over from the reference's launch shape
+                import warnings
+                warnings.warn(log)
+            return ""
+        return log or "compile failed"
 
     def chunk_sides(self, ptr: int, num_bytes: int) -> bytes:
         n = (num_bytes + (ptr & 4095) + 4095) // 4096

@@ -377,6 +377,8 @@ SA_API int sideaware_create_kernel_advanced(const char* header, bool precompile,
 SA_API int sideaware_compile_check(const char* header, int wide, char* log_out, size_t log_capacity) {
     std::string why;
     bool ok = sa_jit_compile_only(header, wide != 0, &why);
+    const std::string warn = sa_jit_contract_warnings(header); // reported with the log, whether or not the header compiles
+    if (!warn.empty()) why = why.empty() ? warn : warn + "\n" + why;
     if (log_out && log_capacity) {
         std::strncpy(log_out, why.c_str(), log_capacity - 1);
         log_out[log_capacity - 1] = 0;

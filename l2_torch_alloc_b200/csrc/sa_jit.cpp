@@ -95,11 +95,30 @@ struct SaJitDeviceCache {
 SaJitDeviceCache* sa_jit_new_device_cache() { return new SaJitDeviceCache(); }
 void sa_jit_delete_device_cache(SaJitDeviceCache* c) { delete c; }
 
+// Constructs that the reference's launch shape allowed and this one does not: blocks here are one-dimensional
+// (the reference launches (256, groups), sideaware.cu:1407), one WARP owns a 4 KiB chunk and different warps take
+// different numbers of chunks, so a barrier across a 256-thread group or the block can neither be reached by all
+// its threads nor does it delimit a chunk.
+std::string sa_jit_contract_warnings(const char* header) {
+    std::string text(header ? header : ""), out;
+    for (const char* word : {"threadIdx.y", "blockDim.y", "__syncthreads", "bar.sync", "barrier.sync"})
+        if (text.find(word) != std::string::npos) {
+            if (!out.empty()) out += ", ";
+            out += word;
+        }
+    if (out.empty()) return out;
+    return "warning: the functor header uses " + out + "; blocks are one-dimensional here, a warp (not a 256-thread group) owns a "
+           "4 KiB chunk and warps take different numbers of chunks, so group-wide indexing or barriers inside "
+           "vector_op / elementwise_op / indexing do not work as under the reference's (256, groups) launch";
+}
+
 int sa_jit_register(const char* header, int default_groups) {
     std::lock_guard<std::mutex> lock(g_reg_mu);
     std::string text(header);
     auto it = g_ids.find(text);
     if (it != g_ids.end()) return it->second;
+    const std::string warn = sa_jit_contract_warnings(header);
+    if (!warn.empty()) std::fprintf(stderr, "sideaware: %s\n", warn.c_str());
     int id = (int)g_headers.size();
     g_headers.push_back(Header{text, default_groups > 0 ? (default_groups > 4 ? 4 : default_groups) : 4});
     g_ids.emplace(std::move(text), id);

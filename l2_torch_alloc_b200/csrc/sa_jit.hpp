@@ -32,5 +32,7 @@ cudaError_t sa_jit_launch(SaDevice* dev, int id, bool wide, const SaSched& sched
 int sa_jit_max_threads(SaDevice* dev, int id, bool wide, std::string* why);
 // Compiles both variants now; false (and *why) on failure.
 bool sa_jit_precompile(SaDevice* dev, int id, std::string* why);
+// "" or one line naming the constructs in `header` that do not carry over from the reference's launch shape.
+std::string sa_jit_contract_warnings(const char* header);
 // Compiles `header` for sm_100a without loading it (no GPU needed); for build-time checks.
 bool sa_jit_compile_only(const char* header, bool wide, std::string* why);

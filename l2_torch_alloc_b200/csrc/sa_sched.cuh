@@ -34,6 +34,12 @@ typedef unsigned long long sa_u64;
 #define SA_CHUNK_VECS 256u       // 4 KiB chunk in 16-byte vectors
 #define SA_DC_VECS 512u          // 8 KiB double chunk in 16-byte vectors
 #define SA_VEC_PER_LANE 8        // 16-byte vectors each lane of a warp moves per chunk
+#ifndef SA_STATIC_SHARE_PCT
+#define SA_STATIC_SHARE_PCT 60   // large arrays: percentage of the tickets dealt out in the blocks' opening batches
+#endif
+#ifndef SA_DYNAMIC_FROM
+#define SA_DYNAMIC_FROM 4        // per-warp claims are used from this many tickets per warp and side on
+#endif
 
 enum { SA_PLACE_AWARE = 0, SA_PLACE_UNAWARE = 1, SA_PLACE_WRONG = 2 };
 
@@ -142,10 +148,10 @@ SA_HD void sa_sched_grid(SaSched& s, int max_blocks, int warps, int* grid, int s
     }
     const sa_u64 fewer = blocks[0] < blocks[1] ? blocks[0] : blocks[1];
     const sa_u64 M = s.num_tickets;
-    if (M >= 4 * fewer * (sa_u64)warps) {
+    if (M >= (sa_u64)SA_DYNAMIC_FROM * fewer * (sa_u64)warps) {
         s.active_warps = (sa_u32)warps;
         const sa_u64 more = blocks[0] < blocks[1] ? blocks[1] : blocks[0];
-        sa_u64 share = (M * 6 / 10) / (more * (sa_u64)warps);
+        sa_u64 share = (M * SA_STATIC_SHARE_PCT / 100) / (more * (sa_u64)warps);
         s.share = (sa_u32)(share < 1 ? 1 : share);
         s.opening[0] = s.opening[1] = s.share * s.active_warps;
         s.dynamic = 1;
@@ -187,12 +193,16 @@ SA_D sa_u32 sa_lane() { return threadIdx.x & 31u; }
 // Same-address atomics are the scarce resource (an L2 slice retires one every few
 // cycles), so they are kept few and off the critical path:
 //  1. a block opens with ONE atomic that takes opening[side] tickets (at most share x active_warps);
-//     warp w works on tickets base + w, base + w + active_warps, ... (neighbouring warps, neighbouring memory);
+//     warp w works on tickets base + w, base + w + active_warps, ... (neighbouring warps, neighbouring memory;
+//     rotating the warps from round to round, against periodic patterns such as RoPE's V heads, was measured: no gain);
 //  2. for large arrays each warp then claims single tickets for itself, always one ahead of
 //     the ticket it is working on (the result is only looked at after that ticket is done);
 //  3. leftovers of both sides (uneven SM split, a busy SM) are taken by the block as a whole,
 //     one atomic per side per batch of active_warps tickets, both in flight together;
-//  4. one atomic per block counts finished blocks; the last one rewinds the counters.
+//     for small arrays the first sweep's claims are put in flight while warp 0 works on its last dealt ticket, so
+//     finding nothing left costs no round trip of its own;
+//  4. one atomic per block counts finished blocks; the last one rewinds the counters, so a launch leaves its
+//     slot as it found it (a kernel recorded in a CUDA graph can be replayed).
 template <class Body>
 SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& body) {
     __shared__ sa_u32 sa_batch;
@@ -229,6 +239,7 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
     // phase 0 = tickets dealt from the opening batch, 1 = own claims, 2 = block-wide leftovers.
     sa_u32 phase = active ? 0u : 2u;
     sa_u32 dealt = 0, pending = none, second = none;
+    sa_u32 early_own = none, early_other = none; // thread 0: claims of the first sweep, issued ahead of it
 #pragma unroll 1
     for (;;) {
         sa_u32 t = none, side = my_side;
@@ -241,6 +252,12 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
             t = base + mine;
             ++dealt;
             if (s.dynamic && dealt == s.share) pending = claim_issue(); // overlaps the last dealt ticket
+            if (!s.dynamic && threadIdx.x == 0 && (dealt == s.share || mine + s.active_warps >= s.opening[my_side])) {
+                // warp 0 is starting on its last dealt ticket: by now every block that runs has taken its opening
+                // batch, so the first sweep will normally find nothing; its two claims travel during this ticket
+                early_own = atomicAdd(own, s.active_warps);
+                early_other = atomicAdd(other, s.active_warps);
+            }
         } else if (phase == 1u) {
             t = __shfl_sync(0xffffffffu, pending, 0);
             if (t >= M) {
@@ -257,8 +274,15 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
             __syncthreads(); // everybody has finished with the previous batch numbers
             if (threadIdx.x == 0) {
                 // the two claims travel together, so finding nothing left costs one round trip
-                sa_u32 a = atomicAdd(own, s.active_warps);
-                sa_u32 b = atomicAdd(other, s.active_warps);
+                sa_u32 a, b;
+                if (early_own != none) {
+                    a = early_own;
+                    b = early_other;
+                    early_own = none;
+                } else {
+                    a = atomicAdd(own, s.active_warps);
+                    b = atomicAdd(other, s.active_warps);
+                }
                 sa_batch = a;
                 sa_batch_other = b;
             }

@@ -1,7 +1,7 @@
 """Small, self-terminating workloads for profiler captures.
 
     python -m tests.profile_case memcpy   [--mib 256] [--reps 4] [--placement aware]
-    python -m tests.profile_case rope     [--batch 2]  [--reps 4]
+    python -m tests.profile_case rope     [--batch 2]  [--reps 4] [--rope-engine 0]
     python -m tests.profile_case functor  [--mib 256] [--reps 4]
     python -m tests.profile_case functor-jit [--mib 256] [--reps 4]   (the same functor through NVRTC)
     python -m tests.profile_case mxfp8    [--mib 256] [--reps 3]      (bf16 -> MXFP8 functor; --mib is the input size)
@@ -28,10 +28,12 @@ def main():
     ap.add_argument("--reps", type=int, default=4)
     ap.add_argument("--placement", default="aware", choices=["aware", "unaware", "wrong"])
     ap.add_argument("--engine", type=int, default=1, help="memcpy engine: 1 = bulk copies (default), 0 = vector")
+    ap.add_argument("--rope-engine", type=int, default=0, help="RoPE engine: 0 = vector (default), 1 = staged through shared memory")
     args = ap.parse_args()
     sa = pkg.SideAware()
     sa.set_placement(args.placement)
     sa.lib.sideaware_set_memcpy_engine(args.engine)
+    sa.lib.sideaware_set_rope_engine(args.rope_engine)
     torch.cuda.set_device(0)
     if args.case == "growth":
         import json

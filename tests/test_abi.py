@@ -195,3 +195,20 @@ def test_headers_compile_as_c_and_together_as_cxx(tmp_path):
     cxx_file = tmp_path / "both.cpp"
     cxx_file.write_text('#include "sideaware.h"\n#include "sideaware_alloc.h"\n#include "sideaware.h"\nint main() { sideaware_stats_t s; (void)s; return 0; }\n')
     subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", inc, "-c", str(cxx_file), "-o", str(tmp_path / "b.o")], check=True)
+
+
+def test_compile_check_warns_about_group_wide_constructs():
+    """Blocks are one-dimensional and a warp owns a chunk: a header that indexes by threadIdx.y or synchronises a
+    256-thread group (uses the reference's launch shape allowed, sideaware.cu:83, :1407) is reported when it is checked."""
+    import ctypes
+    import l2_torch_alloc_b200 as pkg
+    from l2_torch_alloc_b200 import functors
+    sa = pkg.SideAware()
+    buf = ctypes.create_string_buffer(1 << 14)
+    assert sa.lib.sideaware_compile_check(functors.MEMCPY.encode(), 0, buf, len(buf)) == 0 and buf.value == b""
+    grouped = functors.MEMCPY.replace("out0 = in0;", "out0 = in0 + (int)threadIdx.y; __syncthreads();")
+    assert sa.lib.sideaware_compile_check(grouped.encode(), 0, buf, len(buf)) == 0  # it still compiles
+    text = buf.value.decode()
+    assert "warning" in text and "threadIdx.y" in text and "__syncthreads" in text
+    with pytest.warns(UserWarning, match="one-dimensional"):
+        assert sa.compile_check(grouped) == ""

@@ -202,3 +202,41 @@ def test_more_streams_than_rings_can_ever_be_made(sa):
     for p in (src, dst):
         sa.free(p)
     destroy_streams(streams)
+
+
+@pytest.mark.parametrize("engine", [1, 0])
+def test_launches_recorded_in_a_cuda_graph_can_be_replayed(sa, engine):
+    """A launch leaves its ticket counters as it found them (the last block to finish rewinds them), so kernels
+    recorded in a CUDA graph give the right result every time the graph is replayed: a copy and an in-place RoPE
+    captured once, replayed four times on fresh data."""
+    import torch
+    from oracle import oracle
+    sa.lib.sideaware_set_memcpy_engine(engine)
+    n = (40 << 20) + 4096 + 16
+    src = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    B, T, Nq, Nkv, HS = 2, 128, 8, 2, 64
+    x_host = np.random.default_rng(5).uniform(-1, 1, size=(B, T, Nq + 2 * Nkv, HS)).astype(np.float32)
+    table = oracle.freqs_cis(HS, T, 10000.0, 0)
+    want = torch.from_numpy(oracle.rope_forward_f32(x_host, table, B, T, Nq, Nkv, HS)).cuda()
+    x0 = torch.from_numpy(x_host).cuda()
+    x = x0.clone()
+    tab = torch.from_numpy(table).cuda()
+    # once outside the capture: first use of a stream's counters and of the kernels' attributes
+    sa.memcpy(dst, src)
+    sa.rope_forward(x, tab, Nq, Nkv)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sa.memcpy(dst, src)
+        sa.rope_forward(x, tab, Nq, Nkv)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    for _ in range(4):
+        src.copy_(torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=gen))
+        dst.zero_()
+        x.copy_(x0)
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(dst, src)
+        assert torch.equal(x, want)
+    assert sa.error_count() == 0 or "ticket" not in sa.last_error()
