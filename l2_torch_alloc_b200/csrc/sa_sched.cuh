@@ -199,8 +199,7 @@ SA_D sa_u32 sa_lane() { return threadIdx.x & 31u; }
 //     the ticket it is working on (the result is only looked at after that ticket is done);
 //  3. leftovers of both sides (uneven SM split, a busy SM) are taken by the block as a whole,
 //     one atomic per side per batch of active_warps tickets, both in flight together;
-//     for small arrays the first sweep's claims are put in flight while warp 0 works on its last dealt ticket, so
-//     finding nothing left costs no round trip of its own;
+//     (putting the first sweep's claims in flight during a warp's last dealt ticket was measured: no gain);
 //  4. one atomic per block counts finished blocks; the last one rewinds the counters, so a launch leaves its
 //     slot as it found it (a kernel recorded in a CUDA graph can be replayed).
 template <class Body>
@@ -239,7 +238,6 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
     // phase 0 = tickets dealt from the opening batch, 1 = own claims, 2 = block-wide leftovers.
     sa_u32 phase = active ? 0u : 2u;
     sa_u32 dealt = 0, pending = none, second = none;
-    sa_u32 early_own = none, early_other = none; // thread 0: claims of the first sweep, issued ahead of it
 #pragma unroll 1
     for (;;) {
         sa_u32 t = none, side = my_side;
@@ -252,12 +250,6 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
             t = base + mine;
             ++dealt;
             if (s.dynamic && dealt == s.share) pending = claim_issue(); // overlaps the last dealt ticket
-            if (!s.dynamic && threadIdx.x == 0 && (dealt == s.share || mine + s.active_warps >= s.opening[my_side])) {
-                // warp 0 is starting on its last dealt ticket: by now every block that runs has taken its opening
-                // batch, so the first sweep will normally find nothing; its two claims travel during this ticket
-                early_own = atomicAdd(own, s.active_warps);
-                early_other = atomicAdd(other, s.active_warps);
-            }
         } else if (phase == 1u) {
             t = __shfl_sync(0xffffffffu, pending, 0);
             if (t >= M) {
@@ -274,15 +266,8 @@ SA_D void sa_for_each_chunk(const SaSched& s, const SaSideTable& sides, Body&& b
             __syncthreads(); // everybody has finished with the previous batch numbers
             if (threadIdx.x == 0) {
                 // the two claims travel together, so finding nothing left costs one round trip
-                sa_u32 a, b;
-                if (early_own != none) {
-                    a = early_own;
-                    b = early_other;
-                    early_own = none;
-                } else {
-                    a = atomicAdd(own, s.active_warps);
-                    b = atomicAdd(other, s.active_warps);
-                }
+                sa_u32 a = atomicAdd(own, s.active_warps);
+                sa_u32 b = atomicAdd(other, s.active_warps);
                 sa_batch = a;
                 sa_batch_other = b;
             }
