@@ -10,9 +10,12 @@
 // Differences: every SM probes many addresses (signature matrix analysed on the
 // host, see sa_topology.cpp), pages are probed by all SMs in parallel with two
 // votes per page, and no kernel waits on another block.
+#include <unistd.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -197,6 +200,51 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
     if ((e = cudaMemcpy(p->offsets, offsets.data(), sz_off, cudaMemcpyHostToDevice)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "upload offsets"); }
     if ((e = cudaMemset(p->lat, 0xff, sz_lat)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "cudaMemset(lat)"); }
 
+    // Topology cache (off unless SIDEAWARE_TOPOLOGY_CACHE names a directory): what an earlier process found on this
+    // very GPU under this driver, confirmed before use by re-measuring the 64 probe addresses (one launch of about
+    // 40 us) against what the file claims: sides of the SMs, their thresholds and the hash at once.
+    std::string cache_path, gpu_uuid;
+    int driver_version = 0;
+    if (const char* dir = std::getenv("SIDEAWARE_TOPOLOGY_CACHE")) {
+        char hex[33];
+        for (int i = 0; i < 16; ++i) std::snprintf(hex + 2 * i, 3, "%02x", (unsigned)(unsigned char)prop.uuid.bytes[i]);
+        gpu_uuid = hex;
+        cudaDriverGetVersion(&driver_version);
+        cache_path = std::string(dir) + "/sideaware-" + gpu_uuid + ".topo";
+        std::string text, reason;
+        if (FILE* f = std::fopen(cache_path.c_str(), "rb")) {
+            char buf[4096];
+            size_t got;
+            while ((got = std::fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, got);
+            std::fclose(f);
+            SaTopology cached;
+            if (!sa_topology_parse(text, gpu_uuid, driver_version, topo->num_sms, &cached, &reason)) {
+                std::fprintf(stderr, "sideaware: topology cache %s not used: %s\n", cache_path.c_str(), reason.c_str());
+            } else if (!cached.hash_usable) {
+                // nothing worth keeping: discover again
+            } else {
+                cached.device = device;
+                std::vector<uint64_t> addrs(kNumAddr);
+                for (int j = 0; j < kNumAddr; ++j) addrs[j] = probe_page_va + offsets[j];
+                std::vector<uint8_t> measured(kNumAddr);
+                int ambiguous = 0, wrong = 0;
+                e = sa_probe_sides(p, cached, addrs.data(), kNumAddr, measured.data(), nullptr, &ambiguous);
+                if (e != cudaSuccess) { sa_probe_destroy(p); return fail(e, "spot check of the cached topology"); }
+                for (int j = 0; j < kNumAddr; ++j) wrong += measured[j] != (measured[0] ^ sa_parity32(offsets[j] & cached.hash));
+                if (wrong <= 1 && ambiguous <= 2) {
+                    *topo = cached;
+                    topo->from_cache = true;
+                    topo->discovery_passes = 0;
+                    if ((e = cudaMemcpy(p->gpu_side_index, topo->side_index, SA_MAX_SM, cudaMemcpyHostToDevice)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "upload side index"); }
+                    *out = p;
+                    return cudaSuccess;
+                }
+                std::fprintf(stderr, "sideaware: topology cache %s not used: %d of %d re-measured addresses disagree with it (%d ambiguous)\n",
+                             cache_path.c_str(), wrong, kNumAddr, ambiguous);
+            }
+        }
+    }
+
     // more than half of an SM's shared memory per block: at most one block resident per SM
     int smem = (int)std::min<size_t>(prop.sharedMemPerBlockOptin, 120 * 1024);
     if (smem > 48 * 1024) cudaFuncSetAttribute(sa_discover_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -227,6 +275,15 @@ cudaError_t sa_probe_create(int device, uint64_t probe_page_va, SaProbeDevice** 
         if ((int)row_smid.size() >= topo->num_sms && topo->hash_usable && topo->confidence >= 0.95) break;
     }
     if ((e = cudaMemcpy(p->gpu_side_index, topo->side_index, SA_MAX_SM, cudaMemcpyHostToDevice)) != cudaSuccess) { sa_probe_destroy(p); return fail(e, "upload side index"); }
+    if (!cache_path.empty() && topo->hash_usable) { // written whole or not at all: temporary name, then rename
+        const std::string tmp = cache_path + ".tmp" + std::to_string((long long)getpid());
+        if (FILE* f = std::fopen(tmp.c_str(), "wb")) {
+            const std::string text = sa_topology_serialize(*topo, gpu_uuid, driver_version);
+            const bool ok = std::fwrite(text.data(), 1, text.size(), f) == text.size();
+            if (std::fclose(f) == 0 && ok) std::rename(tmp.c_str(), cache_path.c_str());
+            else std::remove(tmp.c_str());
+        }
+    }
     *out = p;
     return cudaSuccess;
 }

@@ -26,6 +26,7 @@ struct SaTopology {
     double confidence = 0.0;      // min over SMs of |hamming - n/2| / (n/2)
     uint32_t thr[SA_MAX_SM] = {0}, near_lat[SA_MAX_SM] = {0}, far_lat[SA_MAX_SM] = {0};
     std::string json;             // raw data for diagnostics
+    bool from_cache = false;      // taken from a topology cache file (and confirmed by a spot check), not discovered
 };
 
 struct SaProbeDevice; // device-side buffers, opaque
@@ -58,3 +59,10 @@ uint32_t* sa_probe_wait_error_word(SaProbeDevice* p);
 // offsets[1..17] == 1<<4 .. 1<<20, the rest are validation offsets.
 void sa_analyse_latency_matrix(const std::vector<uint32_t>& lat, int num_rows, const std::vector<int>& row_smid,
                                const std::vector<uint32_t>& offsets, SaTopology* topo);
+
+// Topology cache (text; pure functions, exposed for CPU tests).  A file is accepted only if it was written for the
+// same GPU (UUID), driver version and SM count, is complete (checksum) and consistent in itself; the caller then
+// confirms it by measurement before use.
+std::string sa_topology_serialize(const SaTopology& t, const std::string& gpu_uuid, int driver_version);
+bool sa_topology_parse(const std::string& text, const std::string& gpu_uuid, int driver_version, int num_sms,
+                       SaTopology* out, std::string* why);

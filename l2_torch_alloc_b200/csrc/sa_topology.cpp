@@ -172,3 +172,83 @@ void sa_analyse_latency_matrix(const std::vector<uint32_t>& lat, int num_rows, c
     js << "]}";
     T.json = js.str();
 }
+
+// ---------------------------------------------------------------------------
+// Topology cache: what discovery found, as text, keyed by the GPU it was found on
+// ---------------------------------------------------------------------------
+// The reference probes every device on every start (sideaware.cu:837-868).  Discovery here takes a few
+// milliseconds; a program that starts often can keep its result in a file.  A cached topology is only a
+// CLAIM: the caller re-measures a handful of addresses against it before using it (sa_probe.cu), and the key
+// (GPU UUID, driver version, SM count, format version) must match to the letter.
+static const char kCacheMagic[] = "sideaware-topology-v1";
+
+std::string sa_topology_serialize(const SaTopology& t, const std::string& gpu_uuid, int driver_version) {
+    std::ostringstream o;
+    o << kCacheMagic << "\n";
+    o << "uuid " << gpu_uuid << "\n";
+    o << "driver " << driver_version << "\n";
+    o << "num_sms " << t.num_sms << "\n";
+    o << "max_smid " << t.max_smid << "\n";
+    o << "hash " << t.hash << "\n";
+    o << "hash_usable " << (t.hash_usable ? 1 : 0) << "\n";
+    o << "validation " << t.validation_offsets << " " << t.validation_errors << "\n";
+    o << "confidence " << (long long)std::llround(t.confidence * 1e6) << "\n";
+    o << "count " << t.count[0] << " " << t.count[1] << " " << t.min_per_side << "\n";
+    unsigned long long sum = 0;
+    for (int sm = 0; sm < SA_MAX_SM; ++sm) {
+        o << "sm " << sm << " " << (int)t.side_index[sm] << " " << t.thr[sm] << " " << t.near_lat[sm] << " " << t.far_lat[sm] << "\n";
+        sum = sum * 1000003ull + t.side_index[sm] + 7ull * t.thr[sm] + 13ull * t.near_lat[sm] + 17ull * t.far_lat[sm];
+    }
+    o << "check " << (sum ^ t.hash) << "\n";
+    return o.str();
+}
+
+bool sa_topology_parse(const std::string& text, const std::string& gpu_uuid, int driver_version, int num_sms,
+                       SaTopology* out, std::string* why) {
+    auto fail = [&](const char* w) {
+        if (why) *why = w;
+        return false;
+    };
+    std::istringstream in(text);
+    std::string word;
+    if (!(in >> word) || word != kCacheMagic) return fail("not a topology cache file of this format");
+    SaTopology t;
+    std::string uuid;
+    long long driver = -1, usable = -1, conf = -1;
+    if (!(in >> word >> uuid) || word != "uuid") return fail("malformed (uuid)");
+    if (uuid != gpu_uuid) return fail("written for another GPU");
+    if (!(in >> word >> driver) || word != "driver") return fail("malformed (driver)");
+    if (driver != driver_version) return fail("written under another driver version");
+    if (!(in >> word >> t.num_sms) || word != "num_sms") return fail("malformed (num_sms)");
+    if (t.num_sms != num_sms || num_sms <= 0 || num_sms > SA_MAX_SM) return fail("SM count differs");
+    if (!(in >> word >> t.max_smid) || word != "max_smid" || t.max_smid < 0 || t.max_smid >= SA_MAX_SM) return fail("malformed (max_smid)");
+    if (!(in >> word >> t.hash) || word != "hash") return fail("malformed (hash)");
+    if (!(in >> word >> usable) || word != "hash_usable" || (usable != 0 && usable != 1)) return fail("malformed (hash_usable)");
+    t.hash_usable = usable == 1;
+    if (!(in >> word >> t.validation_offsets >> t.validation_errors) || word != "validation") return fail("malformed (validation)");
+    if (!(in >> word >> conf) || word != "confidence" || conf < 0 || conf > 1000000) return fail("malformed (confidence)");
+    t.confidence = conf / 1e6;
+    if (!(in >> word >> t.count[0] >> t.count[1] >> t.min_per_side) || word != "count") return fail("malformed (count)");
+    unsigned long long sum = 0;
+    int ones = 0, zeros = 0;
+    for (int sm = 0; sm < SA_MAX_SM; ++sm) {
+        int idx = -1, side = -1;
+        if (!(in >> word >> idx >> side >> t.thr[sm] >> t.near_lat[sm] >> t.far_lat[sm]) || word != "sm" || idx != sm || side < 0 || side > 255)
+            return fail("malformed (per-SM line)");
+        t.side_index[sm] = (uint8_t)side;
+        if (sm <= t.max_smid) (side & 1 ? ones : zeros)++;
+        sum = sum * 1000003ull + t.side_index[sm] + 7ull * t.thr[sm] + 13ull * t.near_lat[sm] + 17ull * t.far_lat[sm];
+    }
+    unsigned long long check = 0;
+    if (!(in >> word >> check) || word != "check" || check != (sum ^ t.hash)) return fail("checksum mismatch (truncated or edited file)");
+    // what the numbers claim must hang together before anything is measured against them
+    if (t.count[0] + t.count[1] != t.num_sms || t.min_per_side != std::min(t.count[0], t.count[1])) return fail("SM counts do not add up");
+    if (t.hash_usable && (!(t.hash & 4096u) || (t.hash & 4095u) || (t.hash & ~0x1FFFF0u))) return fail("hash marked usable but not of the required form");
+    (void)ones;
+    (void)zeros;
+    t.json = "{\"from_cache\":true,\"num_sms\":" + std::to_string(t.num_sms) + ",\"sms_seen\":" + std::to_string(t.num_sms) +
+             ",\"hash\":" + std::to_string(t.hash) + ",\"hash_usable\":" + (t.hash_usable ? "true" : "false") +
+             ",\"side0\":" + std::to_string(t.count[0]) + ",\"side1\":" + std::to_string(t.count[1]) + "}";
+    *out = t;
+    return true;
+}

@@ -6,6 +6,7 @@
 //   ring      stage bookkeeping of the bulk-copy kernels, with loads that never arrive
 // Usage: test_core <sched|alloc|chunks|topology|ring|all>
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -960,6 +961,57 @@ static void test_topology() {
     topo_case(0x1EF000u, 148, 300, 0, false, false);    // no near/far difference at all: must refuse
     topo_case(0x1EE000u, 148, 300, 3000, false, false); // 8 KiB granularity: chunk pairing would not hold
     topo_case(0x1EF800u, 148, 300, 3000, false, false); // side flips inside a 4 KiB chunk
+    {   // topology cache: a file is believed only if it is complete, consistent and written for this very GPU and driver
+        SaTopology t;
+        t.num_sms = 148;
+        t.max_smid = 147;
+        t.hash = 0x1EF000u;
+        t.hash_usable = true;
+        t.validation_offsets = 46;
+        t.confidence = 0.987654;
+        int ord[2] = {0, 0};
+        for (int sm = 0; sm < 148; ++sm) {
+            const int side = (sm / 2) % 2 == 0 ? 0 : 1;
+            t.side_index[sm] = (uint8_t)(side | (ord[side]++ << 1));
+            t.thr[sm] = 500 + sm;
+            t.near_lat[sm] = 330 + sm % 7;
+            t.far_lat[sm] = 760 + sm % 5;
+        }
+        t.count[0] = ord[0];
+        t.count[1] = ord[1];
+        t.min_per_side = std::min(ord[0], ord[1]);
+        const std::string uuid = "00112233445566778899aabbccddeeff";
+        const std::string text = sa_topology_serialize(t, uuid, 12090);
+        SaTopology back;
+        std::string why;
+        CHECK(sa_topology_parse(text, uuid, 12090, 148, &back, &why));
+        CHECK(back.hash == t.hash && back.hash_usable && back.count[0] == t.count[0] && back.count[1] == t.count[1]);
+        CHECK(std::memcmp(back.side_index, t.side_index, SA_MAX_SM) == 0 && std::memcmp(back.thr, t.thr, sizeof(t.thr)) == 0);
+        CHECK(std::memcmp(back.near_lat, t.near_lat, sizeof(t.near_lat)) == 0 && std::memcmp(back.far_lat, t.far_lat, sizeof(t.far_lat)) == 0);
+        CHECK(std::fabs(back.confidence - t.confidence) < 1e-6 && back.max_smid == 147);
+        CHECK(!sa_topology_parse(text, "ffffffffffffffffffffffffffffffff", 12090, 148, &back, &why) && why.find("another GPU") != std::string::npos);
+        CHECK(!sa_topology_parse(text, uuid, 12080, 148, &back, &why) && why.find("driver") != std::string::npos);
+        CHECK(!sa_topology_parse(text, uuid, 12090, 132, &back, &why) && why.find("SM count") != std::string::npos);
+        CHECK(!sa_topology_parse(text.substr(0, text.size() / 2), uuid, 12090, 148, &back, &why));       // truncated
+        CHECK(!sa_topology_parse("", uuid, 12090, 148, &back, &why));
+        CHECK(!sa_topology_parse("something else entirely\n", uuid, 12090, 148, &back, &why));
+        std::string edited = text;
+        const size_t at = edited.find("sm 17 ");
+        CHECK(at != std::string::npos);
+        edited[at + 6] = edited[at + 6] == '1' ? '0' : '1';                                             // one SM moved to the other side
+        CHECK(!sa_topology_parse(edited, uuid, 12090, 148, &back, &why) && why.find("checksum") != std::string::npos);
+        std::string other_hash = text;
+        const size_t h = other_hash.find("hash 2027520");
+        CHECK(h != std::string::npos);
+        other_hash.replace(h, 12, "hash 2023424"); // 0x1EE000: 8 KiB granularity
+        CHECK(!sa_topology_parse(other_hash, uuid, 12090, 148, &back, &why));
+        SaTopology broken = t;
+        broken.count[0] += 1; // counts that do not add up, with a checksum that is right
+        CHECK(!sa_topology_parse(sa_topology_serialize(broken, uuid, 12090), uuid, 12090, 148, &back, &why) && why.find("add up") != std::string::npos);
+        broken = t;
+        broken.hash = 0x1EE000u; // marked usable but side would not flip every 4 KiB
+        CHECK(!sa_topology_parse(sa_topology_serialize(broken, uuid, 12090), uuid, 12090, 148, &back, &why) && why.find("required form") != std::string::npos);
+    }
     std::printf("topology: done\n");
 }
 

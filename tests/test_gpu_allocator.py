@@ -228,6 +228,50 @@ def test_mapping_ahead_of_need(sa):
         sa.lib.sideaware_release_unused()
 
 
+def test_topology_cache_is_confirmed_before_use(tmp_path):
+    """SIDEAWARE_TOPOLOGY_CACHE: the second process on the same GPU takes the topology from the file the first one
+    wrote, after re-measuring 64 addresses against it; a file that claims another hash is rejected by that
+    measurement and discovery runs again.  The reference probes on every start (sideaware.cu:837-868)."""
+    import glob
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SIDEAWARE_TOPOLOGY_CACHE=str(tmp_path))
+
+    def run():
+        r = subprocess.run([sys.executable, os.path.join(root, "tests", "topology_cache_script.py")], capture_output=True,
+                           text=True, timeout=600, cwd=root, env=env)
+        lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+        assert r.returncode == 0 and lines, r.stdout[-2000:] + r.stderr[-2000:]
+        return json.loads(lines[-1][7:]), r.stderr
+
+    first, _ = run()
+    files = glob.glob(os.path.join(str(tmp_path), "sideaware-*.topo"))
+    assert not first["from_cache"] and len(files) == 1
+    second, _ = run()
+    assert second["from_cache"], "the file written by the first process was not used"
+    assert second["summary"] == first["summary"] and second["side_index"] == first["side_index"]
+    assert second["chunks_on_the_wrong_side"] <= 3 and first["chunks_on_the_wrong_side"] <= 3
+    print(f"first use of the device: {first['init_ms']:.1f} ms with discovery, {second['init_ms']:.1f} ms from the cache")
+    # a file that is complete and consistent in itself but wrong about the hash: caught by the spot check
+    sys.path.insert(0, root)
+    text = open(files[0]).read()
+    assert "hash 2027520" in text  # 0x1EF000, what B200 has shown so far; the edit below needs another valid mask
+    lines = text.splitlines()
+    body = [l for l in lines if not l.startswith("check ")]
+    old_check = int([l for l in lines if l.startswith("check ")][0].split()[1])
+    new_hash = 0x1ED000
+    body = [("hash %d" % new_hash) if l.startswith("hash ") and not l.startswith("hash_usable") else l for l in body]
+    body.append("check %d" % ((old_check ^ 2027520) ^ new_hash))
+    open(files[0], "w").write("\n".join(body) + "\n")
+    third, err = run()
+    assert not third["from_cache"] and "disagree" in err
+    assert third["summary"] == first["summary"]
+    fourth, _ = run()  # the third process wrote a good file again
+    assert fourth["from_cache"] and fourth["summary"] == first["summary"]
+
+
 def test_compressible_memory_option(sa):
     """sideaware_compression(true): pages are created compressible where the device supports it
     (sideaware.cu:817-834, :940); kept apart from plain pages; data round-trips unchanged."""
