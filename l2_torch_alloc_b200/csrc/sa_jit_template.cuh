@@ -86,21 +86,33 @@ __device__ __forceinline__ bool indexing(size_type vec_idx, int n, size_type& id
 }
 #endif
 
+// EVICT (input_evict[i] = 1): streaming load, the line is first in line for eviction (data used once).
+// Otherwise an ordinary load that may stay in L1 and L2: what a functor wants for a table that many vectors share
+// (a RoPE cos/sin row is read by every head of a token).  The reference uses ld.global.cg for these
+// (sideaware.cu:140-168), which skips L1; the values loaded are the same.
 template <bool EVICT, typename T>
 __device__ __forceinline__ void sa_load(sa_pack<T>& dst, const sa_pack<T>* base, size_type idx) {
     if constexpr (sa_used<T>) {
         const sa_pack<T>* p = base + idx;
-        if constexpr (sizeof(sa_pack<T>) == 16) {
-            int4 r = EVICT ? __ldcs((const int4*)p) : __ldcg((const int4*)p);
+        if constexpr (sizeof(sa_pack<T>) == 32 || sizeof(sa_pack<T>) == 64) {
+            // an array whose element is wider than the tracked one's (fp32 table beside bf16 data): 16-byte pieces
+            // (every array starts on a 16-byte boundary, the launcher checks that)
+#pragma unroll
+            for (int k = 0; k < (int)sizeof(sa_pack<T>) / 16; ++k) {
+                int4 r = EVICT ? __ldcs((const int4*)p + k) : *((const int4*)p + k);
+                *((int4*)&dst + k) = r;
+            }
+        } else if constexpr (sizeof(sa_pack<T>) == 16) {
+            int4 r = EVICT ? __ldcs((const int4*)p) : *(const int4*)p;
             *(int4*)&dst = r;
         } else if constexpr (sizeof(sa_pack<T>) == 8) {
-            int2 r = EVICT ? __ldcs((const int2*)p) : __ldcg((const int2*)p);
+            int2 r = EVICT ? __ldcs((const int2*)p) : *(const int2*)p;
             *(int2*)&dst = r;
         } else if constexpr (sizeof(sa_pack<T>) == 4) {
-            int r = EVICT ? __ldcs((const int*)p) : __ldcg((const int*)p);
+            int r = EVICT ? __ldcs((const int*)p) : *(const int*)p;
             *(int*)&dst = r;
         } else if constexpr (sizeof(sa_pack<T>) == 2) {
-            short r = EVICT ? __ldcs((const short*)p) : __ldcg((const short*)p);
+            short r = EVICT ? __ldcs((const short*)p) : *(const short*)p;
             *(short*)&dst = r;
         } else {
             dst = *p;

@@ -50,6 +50,9 @@ def rope_forward(T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, bf16: b
     pair_t = "__nv_bfloat162" if bf16 else "float2"
     to_f = ("float x = __low2float(in0), y = __high2float(in0);" if bf16 else "float x = in0.x, y = in0.y;")
     from_f = ("out0 = __floats2bfloat162_rn(re, im);" if bf16 else "out0.x = re; out0.y = im;")
+    # bf16: a 16-byte data vector needs 32 bytes of table; four vectors with their entries in flight per lane need more
+    # than the 64 registers of a 1024-thread block, so blocks of 768 threads.  fp32: the default shape is the fastest.
+    launch = ("#define UNROLLED 4\n#define LAUNCH_BOUNDS __launch_bounds__(768, 1)" if bf16 else "#define UNROLLED 2")
     return f"""
 #include <cuda_bf16.h>
 typedef {pair_t} o0;
@@ -57,9 +60,9 @@ typedef {pair_t} i0;
 typedef float2 i1;
 struct unused {{}};
 typedef unused o1, o2, o3, i2, i3;
-#define UNROLLED 2
+{launch}
 constexpr bool reverse_order = false;
-constexpr bool input_evict[4] = {{1, 0, 0, 0}};
+constexpr bool input_evict[4] = {{1, 0, 0, 0}}; // the table is shared by all heads of a token: keep it cached
 constexpr int rope_T = {T};
 constexpr int rope_half = {head_dim // 2};
 constexpr int rope_rotated = {n_q_heads + n_kv_heads};
