@@ -983,6 +983,10 @@ size_t SaAllocator::top_up(void* stream, const SaAllocConfig& cfg) {
 
 bool SaAllocator::prealloc(size_t size, const SaAllocConfig& cfg) {
     std::lock_guard<std::mutex> lock(mu_);
+    const size_t want_pages = round_to_pages(size) / kSaPageBytes;
+    // a free run that holds the size whichever side it has to start on: nothing to do (and its last user's
+    // ordering stays as it is)
+    if (free_by_len_[cfg.compression && comp_ok_].lower_bound(want_pages + 1) != free_by_len_[cfg.compression && comp_ok_].end()) return true;
     // a block of that size, given straight back: what stays is a free run nobody has used
     SaAllocConfig plain = cfg;
     plain.extra_alloc = 0;
