@@ -98,3 +98,35 @@ def test_silu_mul_functor_at_2_pow_30_elements(sa):
         want = oracle.silu_mul_bf16(au, bu, 0.5)
         got = out_aot[off:off + sl].view(torch.int16).cpu().numpy().view(np.uint16)
         assert oracle.ulp_diff_bf16(got, want).max() <= 1
+
+
+def test_mxfp8_functor_at_2_pow_30_elements(sa):
+    """bf16 -> MXFP8 over 2^30 elements.  Size-independent property: a power-of-two factor on the input moves into the
+    block scales and leaves every element byte as it was (x and 4x: same E4M3 bytes, scale bytes two higher).  And
+    slices spread over the array equal the oracle bit for bit."""
+    import torch
+    n = 1 << 30
+    gen = torch.Generator(device="cuda").manual_seed(0xB200 + 8)
+    x = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    step = 1 << 27
+    for off in range(0, n, step):
+        x[off:off + step] = torch.randn(step, device="cuda", generator=gen).to(torch.bfloat16)
+    el = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    sc = torch.zeros(n // 32, dtype=torch.uint8, device="cuda")
+    sa.mxfp8_quantize(el, sc, x)
+    torch.cuda.synchronize()
+    sl = 1 << 20
+    for off in (0, 12345 * 32, n // 3 // 32 * 32, n - sl):
+        xu = x[off:off + sl].view(torch.int16).cpu().numpy().view(np.uint16)
+        want_el, want_sc = oracle.mxfp8_quantize_bf16(xu)
+        assert np.array_equal(el[off:off + sl].cpu().numpy(), want_el)
+        assert np.array_equal(sc[off // 32:(off + sl) // 32].cpu().numpy(), want_sc)
+    el4 = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    sc4 = torch.zeros(n // 32, dtype=torch.uint8, device="cuda")
+    for off in range(0, n, step):
+        x[off:off + step] *= 4  # exact in bf16 (no value is near the top of the range)
+    sa.mxfp8_quantize(el4, sc4, x)
+    torch.cuda.synchronize()
+    for off in range(0, n, step):
+        assert torch.equal(el4[off:off + step], el[off:off + step])
+    assert torch.equal(sc4.to(torch.int16), sc.to(torch.int16) + 2)
