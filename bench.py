@@ -368,11 +368,10 @@ def run_reference(args, ranks):
 def allocator_churn(lib, rt, dev, sp, ops, arm="sideaware"):
     """`ops` seeded malloc/free calls, sizes log-uniform 4 KiB .. 2 GiB rounded up to 16 B, live set capped
     at 32 GiB.  arm "sideaware": sideaware_malloc_auto / sideaware_free_auto (what torch's pluggable allocator
-    calls); for comparison "cudaMallocAsync": the runtime's stream-ordered pool, "torch": torch's own caching
-    allocator through torch.empty (this process has not installed the pluggable allocator)."""
+    calls); for comparison "cudaMallocAsync": the runtime's stream-ordered pool.  The same sequence through
+    torch.empty (pluggable allocator, torch's own caching allocator) runs in tests/allocator_churn_script.py."""
     import ctypes
     import numpy as np
-    import torch
     rng = np.random.default_rng(0xB200 + 5)
     live, live_bytes, peak = [], 0, 0
     t_malloc_small, t_malloc_large, t_free = [], [], []
@@ -382,18 +381,11 @@ def allocator_churn(lib, rt, dev, sp, ops, arm="sideaware"):
         if arm == "cudaMallocAsync":
             rc = rt.cudaMallocAsync(ctypes.byref(p), size, sp)
             return p.value if rc == 0 else None
-        if arm == "torch":
-            try:
-                return torch.empty(size, dtype=torch.uint8, device="cuda")
-            except torch.OutOfMemoryError:
-                return None
         return lib.sideaware_malloc_auto(size, dev, sp)
 
     def do_free(ptr, size):
         if arm == "cudaMallocAsync":
             rt.cudaFreeAsync(ptr, sp)
-        elif arm == "torch":
-            del ptr  # the caller's reference is dropped as well (see below)
         else:
             lib.sideaware_free_auto(ptr, size, dev, sp)
 
@@ -412,7 +404,7 @@ def allocator_churn(lib, rt, dev, sp, ops, arm="sideaware"):
             t0 = time.perf_counter_ns()
             ptr = do_malloc(size)
             dt = time.perf_counter_ns() - t0
-            if ptr is None or (not isinstance(ptr, torch.Tensor) and not ptr):
+            if not ptr:
                 continue
             (t_malloc_large if size >= (8 << 20) else t_malloc_small).append(dt)
             live.append((ptr, size))
@@ -612,7 +604,7 @@ def e2e_memcpy(c):
     h_dst = torch.empty(MEMCPY_BYTES, dtype=torch.uint8, pin_memory=True)
     h_src.copy_(c.seed_t)
     torch.cuda.synchronize()
-    piece = 64 << 20
+    piece = c.args.e2e_piece_mib << 20
     n_pieces = MEMCPY_BYTES // piece
     s_up, s_k, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     ev_up = [torch.cuda.Event() for _ in range(n_pieces)]
@@ -1052,6 +1044,8 @@ def main():
     ap.add_argument("--no-reference-library", action="store_true",
                     help="skip the comparison runs of the reference's own GPU library (oracle/_ref, N = 1 only)")
     ap.add_argument("--power-seconds", type=float, default=2.0, help="length of each power sampling loop (0 = skip)")
+    ap.add_argument("--e2e-piece-mib", type=int, default=64, choices=[4, 8, 16, 32, 64, 128, 256],
+                    help="piece size of the pipelined end-to-end step (upload / kernel / download overlap piece by piece)")
     ap.add_argument("--check-ranks", action="store_true",
                     help="exercise only the rank plumbing (barrier, max/sum over ranks, rank 0 prints); needs no GPU")
     args = ap.parse_args()
