@@ -48,3 +48,26 @@ inline void elementwise(int kernel_id, size_t num_bytes, void* out0, void* out1 
 }
 
 } // namespace sideaware
+
+// The reference's own wrapper names, at global scope (sideaware.cu:1532-1547): a translation unit that used to
+// `#include "sideaware.cu"` and call sideaware_malloc(&typed_pointer, bytes) inside cudaCheck(...) compiles unchanged
+// against this header (example_llmc_rope.cu:265, :314 does exactly that).  Only where the CUDA runtime's types are
+// known; the kernel launchers need no wrapper, their C declarations take any pointer.
+#if defined(__CUDACC__) || defined(__CUDA_RUNTIME_H__) || defined(__CUDA_RUNTIME_API_H__)
+template <typename T>
+static inline cudaError_t sideaware_malloc(T** dev_ptr, size_t bytes) {
+    return static_cast<cudaError_t>(::sideaware_malloc(reinterpret_cast<void**>(dev_ptr), bytes));
+}
+template <typename T>
+static inline cudaError_t sideaware_malloc_async(T** dev_ptr, size_t bytes, cudaStream_t stream = 0) {
+    return static_cast<cudaError_t>(::sideaware_malloc_async(reinterpret_cast<void**>(dev_ptr), bytes, stream));
+}
+template <typename T>
+static inline cudaError_t sideaware_free(T* ptr) {
+    return static_cast<cudaError_t>(::sideaware_free(const_cast<void*>(static_cast<const void*>(ptr))));
+}
+template <typename T>
+static inline cudaError_t sideaware_free_async(T* ptr, cudaStream_t stream = 0) {
+    return static_cast<cudaError_t>(::sideaware_free_async(const_cast<void*>(static_cast<const void*>(ptr)), stream));
+}
+#endif

@@ -55,8 +55,16 @@ def build(force: bool = False) -> None:
     ):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
     ref_src = reference_tree()
-    wanted = ("libref_rope.so", "sideaware_reference.so") + STAGED_TEXTS
-    if ref_src and (force or not all(os.path.exists(os.path.join(_HERE, "_ref", f)) for f in wanted)):
+    wanted = ("libref_rope.so", "sideaware_reference.so", os.path.join("cxx_example_reference", "rope_example")) + STAGED_TEXTS
+    product = os.path.join(_HERE, "..", "l2_torch_alloc_b200", "sideaware.so")
+    example = os.path.join(_HERE, "_ref", "cxx_example", "rope_example")
+    if os.path.exists(product):  # the reference's C++ example linked against this project's library (make decides if it is stale)
+        wanted += (os.path.join("cxx_example", "rope_example"),)
+    stale = os.path.exists(example) and os.path.exists(product) and any(
+        os.path.getmtime(f) > os.path.getmtime(example)
+        for f in (os.path.join(_HERE, "..", "include", "sideaware.h"), os.path.join(_HERE, "..", "include", "sideaware.hpp"),
+                  os.path.join(_HERE, "sideaware_cu_stand_in.cu")))
+    if ref_src and (force or stale or not all(os.path.exists(os.path.join(_HERE, "_ref", f)) for f in wanted)):
         subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={ref_src}"], stdout=subprocess.DEVNULL)
 
 

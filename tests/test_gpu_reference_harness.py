@@ -94,3 +94,30 @@ def test_reference_rope_header_compiles_for_sm_100a_in_both_index_widths():
             "print('OK')\n") % ROOT
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=STAGED)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(staged(os.path.join("cxx_example", "rope_example"))),
+                    reason="the reference's C++ example has not been built against this library")
+def test_reference_cxx_example_runs_unmodified():
+    """example_llmc_rope.cu as the reference ships it, compiled by oracle/Makefile against this project's headers (its
+    `#include "sideaware.cu"` finds a stand-in that includes sideaware.hpp) and linked to sideaware.so: the program
+    allocates with sideaware_malloc, registers `#include "kernel_rope.cuh"`, validates the result against its own CPU
+    code at six block sizes with its own tolerance, benchmarks, validates its backward kernel and frees."""
+    d = staged("cxx_example")
+    r = subprocess.run([os.path.join(d, "rope_example")], capture_output=True, text=True, timeout=900, cwd=d)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "All results match. Starting benchmarks." in r.stdout and "Backward pass result matches." in r.stdout
+    assert "Mismatch" not in r.stdout
+    times = [float(x) for x in re.findall(r"block_size +\d+ time ([0-9.]+) ms", r.stdout)]
+    assert len(times) == 6
+    print("the reference's example on this library, ms per call with an L2 flush before each:", times)
+    # the same program as the reference builds it (its own sideaware.cu), on the same GPU, where it has been built
+    ref_dir = staged("cxx_example_reference")
+    if os.path.exists(os.path.join(ref_dir, "rope_example")):
+        rr = subprocess.run([os.path.join(ref_dir, "rope_example")], capture_output=True, text=True, timeout=900, cwd=ref_dir)
+        ref_times = [float(x) for x in re.findall(r"block_size +\d+ time ([0-9.]+) ms", rr.stdout)]
+        print("the same example on the reference's own library:", ref_times, "exit code", rr.returncode)
+        if rr.returncode == 0 and len(ref_times) == 6:
+            # level at this small shape (the reference is a few percent ahead on GPUs split 74/74, behind on others)
+            assert min(times) <= 1.06 * min(ref_times)
