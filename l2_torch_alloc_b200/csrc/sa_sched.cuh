@@ -38,7 +38,8 @@ typedef unsigned long long sa_u64;
 #define SA_STATIC_SHARE_PCT 60   // large arrays: percentage of the tickets dealt out in the blocks' opening batches
 #endif
 #ifndef SA_DYNAMIC_FROM
-#define SA_DYNAMIC_FROM 4        // per-warp claims are used from this many tickets per warp and side on
+#define SA_DYNAMIC_FROM 8        // per-warp claims are used from this many tickets per warp and side on (4 measured:
+                                 // 48 MiB copies 9-13 % slower, nothing else faster)
 #endif
 
 enum { SA_PLACE_AWARE = 0, SA_PLACE_UNAWARE = 1, SA_PLACE_WRONG = 2 };
@@ -114,7 +115,8 @@ SA_HD void sa_sched_geometry(SaSched& s, sa_u64 addr, sa_u64 num_vecs, sa_u32 wa
     // one-double-chunk tickets would mean a same-address atomic every ~6 ns per side.  Aim at >= 24
     // tickets per warp and side, 1..8 double chunks (8..64 KiB) per ticket, and at least 2 once the
     // array is large enough for per-warp claims.  A preset dc_per_ticket is kept (kernels that redo
-    // the geometry for another array).
+    // the geometry for another array).  (One-double-chunk tickets for all fully dealt arrays, which
+    // deal out more evenly, were measured: nothing gained at 8-56 MiB, 2-8 % lost at 64-72 MiB.)
     sa_u64 per = s.dc_per_ticket;
     if (per == 0) {
         per = warps_per_side ? s.num_dc / ((sa_u64)warps_per_side * 24u) : 1;
@@ -128,7 +130,7 @@ SA_HD void sa_sched_geometry(SaSched& s, sa_u64 addr, sa_u64 num_vecs, sa_u32 wa
 
 // Host side: grid size and how the tickets are handed out, for a launch with `warps`
 // warps per block on at most `max_blocks` blocks.
-//  * large arrays (>= 4 tickets per warp and side): every warp of every block takes part;
+//  * large arrays (>= 8 tickets per warp and side): every warp of every block takes part;
 //    about 60 % of the tickets are dealt out statically in each block's opening batch, the
 //    rest is claimed ticket by ticket so faster SMs do more;
 //  * small arrays: all tickets are dealt out in the opening batches (the per-ticket atomics
