@@ -422,6 +422,8 @@ def allocator_churn(lib, rt, dev, sp, ops, arm="sideaware"):
     return {"ops": ops, "ops_per_s": ops / elapsed, "seconds": elapsed, "peak_live_gib": peak / 2**30,
             "malloc_small_us_p50": pct(t_malloc_small, 50), "malloc_small_us_p99": pct(t_malloc_small, 99),
             "malloc_large_us_p50": pct(t_malloc_large, 50), "malloc_large_us_p99": pct(t_malloc_large, 99),
+            "malloc_large_us_max": max(t_malloc_large) / 1e3 if t_malloc_large else None,
+            "malloc_large_calls": len(t_malloc_large), "malloc_large_over_5ms": sum(1 for t in t_malloc_large if t > 5e6),
             "free_us_p50": pct(t_free, 50), "free_us_p99": pct(t_free, 99)}
 
 
@@ -958,9 +960,32 @@ def churn_section(c):
     churn["sideaware_direct_calls"] = direct
     churn["sideaware_direct_calls_second_pass"] = second
     churn["driver_call_times"] = c.sa.driver_call_times()
-    c.lib.sideaware_release_unused()
-    c.torch.cuda.synchronize()
+
+    def released():
+        c.lib.sideaware_release_unused()
+        c.torch.cuda.synchronize()
+
+    # First passes depend on what the driver did just before (the first arm after a large release has measured up to
+    # 1.5 x slower than the same arm later), so the two allocators take turns and every run is kept.
+    released()
     churn["cudaMallocAsync"] = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops, arm="cudaMallocAsync")
+    released()
+    # the same first pass with the reference's own knob turned up (sideaware.cu:1475-1478): whenever the mapped set has to
+    # grow it grows by 2 GiB more than asked for, so fewer calls pay for driver work and each of those pays more
+    c.lib.sideaware_prealloc_config(1, 1024)
+    roomy = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops)
+    roomy["prealloc_config"] = {"extra_required": 1, "extra_alloc": 1024}
+    churn["sideaware_direct_calls_2GiB_headroom"] = roomy
+    c.lib.sideaware_prealloc_config(1, 10)
+    released()
+    churn["sideaware_direct_calls_again"] = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops)
+    released()
+    churn["cudaMallocAsync_again"] = allocator_churn(c.lib, c.rt, c.dev, c.sp, ops, arm="cudaMallocAsync")
+    churn["first_pass_seconds"] = {
+        "order": "sideaware, (second pass), cudaMallocAsync, sideaware with 2 GiB headroom, sideaware, cudaMallocAsync",
+        "sideaware": [direct["seconds"], churn["sideaware_direct_calls_again"]["seconds"]],
+        "sideaware_2GiB_headroom": [roomy["seconds"]],
+        "cudaMallocAsync": [churn["cudaMallocAsync"]["seconds"], churn["cudaMallocAsync_again"]["seconds"]]}
     c.torch.cuda.synchronize()
     c.torch.cuda.empty_cache()
     # torch routes, each in a fresh process (the pluggable allocator has to be installed before the first allocation);

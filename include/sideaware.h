@@ -85,6 +85,10 @@ void sideaware_prealloc_config(int extra_required, int extra_alloc);
  * requests up to that size find their pages mapped (about 2 us instead of about 80 us per 2 MiB page).
  * No counterpart in the reference, whose preallocation (sideaware.cu:934-1034) runs only inside a request. */
 sideaware_status_t sideaware_prealloc(size_t bytes, int device);
+/* When the mapped set has to grow and more than start_threshold bytes are mapped but free, free blocks are unmapped,
+ * least recently freed first, down to end_threshold (sideaware.cu:1479-1483; the reference's defaults are 16 GiB and
+ * 2 GiB).  Until this is called the two are at least a half and a quarter of the device's memory: 16 GiB is a ninth
+ * of a B200, and a growing program that crosses it unmaps and maps the same memory again and again. */
 void sideaware_free_mapped_thresholds(size_t start_threshold, size_t end_threshold);
 /* The reference appends a disassembly of each JIT-ed kernel to this file; this
  * library appends the NVRTC log and the generated source instead. */

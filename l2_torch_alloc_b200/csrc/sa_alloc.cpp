@@ -904,7 +904,14 @@ uint64_t SaAllocator::malloc_locked(size_t size, void* stream, const SaAllocConf
     // more than asked for (the reference creates that many spare pages whenever it has to create any,
     // sideaware.cu:1074-1076): the fixed cost of a round of driver calls and measurements is paid less often.
     for (int step = 0; step < 3; ++step) {
-        if (step == 0) trim_locked(cfg.trim_start, cfg.trim_end);
+        if (step == 0) {
+            size_t start = cfg.trim_start, end = cfg.trim_end;
+            if (cfg.trim_scaled && capacity_) {
+                start = std::max(start, capacity_ / 2);
+                end = std::max(end, capacity_ / 4);
+            }
+            trim_locked(start, end);
+        }
         else if (step == 1) trim_locked(0, 0);
         else {
             trim_locked(0, 0);

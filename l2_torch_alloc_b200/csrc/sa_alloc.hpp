@@ -78,6 +78,10 @@ struct SaBackend {
 struct SaAllocConfig {
     size_t trim_start = 16ull << 30; // when the mapped set must grow and more than this is free-but-mapped, unmap
     size_t trim_end = 2ull << 30;    // ... least recently freed runs down to this
+    bool trim_scaled = true;         // the caller has not set the two (sideaware_free_mapped_thresholds): on a device whose
+                                     // size is known they are at least a half and a quarter of its memory (16 and 2 GiB
+                                     // were chosen for 80 GB parts; on 180 GB they make a growing program unmap and
+                                     // map the same memory over and over)
     // sideaware_prealloc_config (sideaware.cu:1475-1478; the reference's top-up rule is :1066-1080), in 2 MiB pages:
     int extra_required = 1;          // after a request has been served, at least this many free pages should still be
                                      // at hand (mapped-and-free, or pooled); if not, the next free() tops them up

@@ -410,6 +410,7 @@ SA_API void sideaware_free_mapped_thresholds(size_t start_threshold, size_t end_
     std::lock_guard<std::mutex> lock(sa_config().mu);
     sa_config().alloc.trim_start = start_threshold;
     sa_config().alloc.trim_end = end_threshold;
+    sa_config().alloc.trim_scaled = false; // the caller's numbers, whatever the device's size
 }
 #ifndef SIDEAWARE_ALLOC_ONLY
 SA_API void sideaware_write_sass(const char* filename) {

@@ -551,6 +551,29 @@ static void test_alloc() {
         uint64_t s = a.malloc(60 * kSaPageBytes, nullptr, cfg); // unbalanced pool: cross-side pages allowed, still correct
         CHECK(s != 0);
     }
+    {   // thresholds nobody set scale with the device: 16 GiB and 2 GiB become a half and a quarter of its memory
+        for (int user_set = 0; user_set < 2; ++user_set) {
+            FakeDriver d;
+            d.capacity_pages = 80 * 512; // 80 GiB
+            SaAllocator a(&d, false, 80ull << 30);
+            SaAllocConfig c2 = cfg;
+            c2.extra_alloc = 0;
+            if (user_set) c2.trim_scaled = false; // what sideaware_free_mapped_thresholds leaves behind
+            std::vector<uint64_t> ps;
+            for (int i = 0; i < 10; ++i) ps.push_back(a.malloc(2ull << 30, nullptr, c2));
+            uint64_t keep = a.malloc(1ull << 30, nullptr, c2);
+            for (uint64_t p : ps) a.free(p, nullptr);        // 20 GiB mapped and free: above 16 GiB, below 40 GiB
+            uint64_t big = a.malloc(21ull << 30, nullptr, c2); // no run is large enough: the mapped set must grow
+            CHECK(big != 0);
+            SaAllocStats st = a.stats();
+            if (user_set) CHECK(st.trims == 1 && st.bytes_cached <= (2ull << 30) + 16 * kSaPageBytes);
+            else CHECK(st.trims == 0 && st.bytes_cached >= (19ull << 30));
+            a.free(big, nullptr);
+            a.free(keep, nullptr);
+            a.release_unused();
+            CHECK(d.live_pages() == 0);
+        }
+    }
     {   // threshold trimming: only when the mapped set must grow; least recently freed runs go first
         FakeDriver d;
         SaAllocator a(&d, false);
