@@ -811,6 +811,22 @@ void SaAllocator::merge_all_free_runs() {
 
 void SaAllocator::trim_locked(size_t start, size_t end) {
     if (cached_bytes_ <= start || cached_bytes_ == 0) return;
+    // What could be given back once neighbouring free runs are merged (they are, after the wait below), by
+    // arithmetic alone: with many short runs between live blocks most free pages belong to chunks that reach into
+    // a neighbour, and a device-wide wait for a trim that then finds nothing to do is the expensive part.
+    size_t could = 0;
+    for (auto it = free_.begin(); it != free_.end();) {
+        const uint64_t va = it->first;
+        Run merged = it->second;
+        auto next = std::next(it);
+        while (next != free_.end() && next->second.seg == merged.seg && next->first == va + merged.pages * kSaPageBytes) {
+            merged.pages += next->second.pages;
+            ++next;
+        }
+        could += reclaimable_pages(va, merged) * kSaPageBytes;
+        it = next;
+    }
+    if (could == 0 || could <= start) return;
     be_->device_sync(); // freed pages may still be in use by queued work
     merge_all_free_runs();
     struct Cand { uint64_t seq, va; size_t pages; };

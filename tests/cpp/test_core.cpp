@@ -574,6 +574,34 @@ static void test_alloc() {
             CHECK(d.live_pages() == 0);
         }
     }
+    {   // free runs that lie across chunk borders can give back little: a miss then neither waits for the device nor trims
+        FakeDriver d;
+        SaAllocator a(&d, false);
+        SaAllocConfig c2 = cfg;
+        c2.extra_alloc = 0;
+        c2.trim_start = 64u << 20;
+        c2.trim_end = 16u << 20;
+        uint64_t whole = a.malloc(100 * kSaPageBytes, nullptr, c2); // one growth: chunks of 7 + 1 pages in a row
+        a.free(whole, nullptr);
+        uint64_t shift = a.malloc(3 * kSaPageBytes, nullptr, c2);   // carved from it: every later block starts 3 pages into a chunk
+        std::vector<uint64_t> ps;
+        for (int i = 0; i < 12; ++i) ps.push_back(a.malloc(16u << 20, nullptr, c2));
+        for (int i = 0; i < 12; i += 2) a.free(ps[i], nullptr); // six runs of 8 pages between live blocks
+        const size_t cached_all = a.stats().bytes_cached;
+        CHECK(cached_all >= (96ull << 20));
+        const int syncs_before = d.syncs;
+        uint64_t big = a.malloc(64u << 20, nullptr, c2); // over the threshold, but only a few whole chunks among the free pages
+        CHECK(big != 0);
+        if (d.model != 1) { // (model 1's irregular sides break the handles up into shorter chunks, which can be given back)
+            CHECK(a.stats().trims == 0 && d.syncs == syncs_before);
+            CHECK(a.stats().bytes_cached >= (96ull << 20));
+        }
+        a.free(big, nullptr);
+        a.free(shift, nullptr);
+        for (int i = 1; i < 12; i += 2) a.free(ps[i], nullptr);
+        a.release_unused();
+        CHECK(d.live_pages() == 0);
+    }
     {   // threshold trimming: only when the mapped set must grow; least recently freed runs go first
         FakeDriver d;
         SaAllocator a(&d, false);
