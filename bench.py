@@ -209,6 +209,33 @@ def time_launches(torch, fn, steps, warmup, ranks=None, per_launch=False):
     return total, each
 
 
+def time_pipeline(torch, step, streams, steps, warmup, ranks=None):
+    """Total ms for `steps` calls of step(), which queues its work on `streams` (not on the current stream): the
+    streams start behind an event on the current stream and the closing event waits for all of them."""
+    cur = torch.cuda.current_stream()
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if ranks:
+        ranks.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(cur)
+    for st_ in streams:
+        st_.wait_event(start)
+    for _ in range(steps):
+        step()
+    for st_ in streams:
+        done = torch.cuda.Event()
+        done.record(st_)
+        cur.wait_event(done)
+    end.record(cur)
+    torch.cuda.synchronize()
+    if ranks:
+        ranks.barrier()
+    return start.elapsed_time(end)
+
+
 def compiled_baseline(torch, fn, nbytes):
     """fn() through torch.compile (inductor), as a comparison line only; the library itself uses no compiler of that kind."""
     try:
@@ -611,25 +638,26 @@ def e2e_memcpy(c):
     s_up, s_k, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     ev_up = [torch.cuda.Event() for _ in range(n_pieces)]
     ev_k = [torch.cuda.Event() for _ in range(n_pieces)]
-    ev_begin, ev_done = torch.cuda.Event(), torch.cuda.Event()
+    ev_down = [torch.cuda.Event() for _ in range(n_pieces)]
 
     def e2e_step():
-        ev_begin.record(c.stream)
-        for st_ in (s_up, s_k, s_down):
-            st_.wait_event(ev_begin)
+        # Steps follow one another like buffers in a stream of work: nothing waits for a whole step, only for what a
+        # piece needs (its upload before its kernel before its download; and, against the step before, the kernel that
+        # read a source piece before that piece is overwritten, the download that read a destination piece likewise).
         for i in range(n_pieces):
             off = i * piece
+            s_up.wait_event(ev_k[i])
             rt.cudaMemcpyAsync(c.src + off, h_src.data_ptr() + off, piece, 1, s_up.cuda_stream)
             ev_up[i].record(s_up)
             s_k.wait_event(ev_up[i])
+            s_k.wait_event(ev_down[i])
             lib.sideaware_memcpy(c.dst + off, c.src + off, piece, c.dev, s_k.cuda_stream)
             ev_k[i].record(s_k)
             s_down.wait_event(ev_k[i])
             rt.cudaMemcpyAsync(h_dst.data_ptr() + off, c.dst + off, piece, 2, s_down.cuda_stream)
-        ev_done.record(s_down)
-        c.stream.wait_event(ev_done)
+            ev_down[i].record(s_down)
 
-    e2e_ms, _ = time_launches(torch, e2e_step, e2e_steps, 2, ranks)
+    e2e_ms = time_pipeline(torch, e2e_step, (s_up, s_k, s_down), e2e_steps, 2, ranks)
     e2e_worst = ranks.max(e2e_ms)
     e2e_value = ranks.world * e2e_steps * 2 * MEMCPY_BYTES / (e2e_worst * 1e-3) / 1e9
     h_dst.zero_()
@@ -639,7 +667,8 @@ def e2e_memcpy(c):
         raise SystemExit("bench: end-to-end copy mismatch")
     return {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": MEMCPY_BYTES, "d2h_bytes_per_step": MEMCPY_BYTES,
             "steps": e2e_steps, "ms_per_step": e2e_worst / e2e_steps,
-            "pipeline": f"{n_pieces} pieces of {piece >> 20} MiB on 3 streams (upload / kernel / download overlap)"}
+            "pipeline": f"{n_pieces} pieces of {piece >> 20} MiB on 3 streams (upload / kernel / download overlap); steps follow "
+                        "one another without a wait in between, every step uploads its input and downloads its result"}
 
 
 def flushed_launch_ms(c, fn, reps, flush_buf):
@@ -834,14 +863,12 @@ def rope_section(c):
             s_up, s_k, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
             ev_up = [torch.cuda.Event() for _ in range(S["B"])]
             ev_k = [torch.cuda.Event() for _ in range(S["B"])]
-            ev_begin, ev_done = torch.cuda.Event(), torch.cuda.Event()
+            ev_down = [torch.cuda.Event() for _ in range(S["B"])]
 
             def e2e_rope_step():
-                ev_begin.record(c.stream)
-                for st_ in (s_up, s_k, s_down):
-                    st_.wait_event(ev_begin)
                 for b in range(S["B"]):
                     off = b * per_b
+                    s_up.wait_event(ev_down[b])  # the step before has read this entry back
                     c.rt.cudaMemcpyAsync(qkv + off, h.data_ptr() + off, per_b, 1, s_up.cuda_stream)
                     ev_up[b].record(s_up)
                     s_k.wait_event(ev_up[b])
@@ -849,13 +876,12 @@ def rope_section(c):
                     ev_k[b].record(s_k)
                     s_down.wait_event(ev_k[b])
                     c.rt.cudaMemcpyAsync(h.data_ptr() + off, qkv + off, per_b, 2, s_down.cuda_stream)
-                ev_done.record(s_down)
-                c.stream.wait_event(ev_done)
+                    ev_down[b].record(s_down)
 
-            ms, _ = time_launches(torch, e2e_rope_step, 4, 1, None)
+            ms = time_pipeline(torch, e2e_rope_step, (s_up, s_k, s_down), 4, 1, None)
             rope["e2e"] = {"value": gbs(moved, ms / 4), "unit": "GB/s (same algorithmic bytes as the kernel figure)",
                            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": ms / 4,
-                           "pipeline": "8 batch entries on 3 streams (upload / kernel / download overlap); V heads travel too"}
+                           "pipeline": "8 batch entries on 3 streams (upload / kernel / download overlap), steps one behind the other without a wait; V heads travel too"}
             del h
 
         # torch eager on the same packed tensor (fp32 math on the q,k heads, written back as bf16), as a baseline
