@@ -1012,6 +1012,9 @@ def churn_section(c):
         "sideaware": [direct["seconds"], churn["sideaware_direct_calls_again"]["seconds"]],
         "sideaware_2GiB_headroom": [roomy["seconds"]],
         "cudaMallocAsync": [churn["cudaMallocAsync"]["seconds"], churn["cudaMallocAsync_again"]["seconds"]]}
+    fp = churn["first_pass_seconds"]
+    fp["best"] = {"sideaware": min(fp["sideaware"]), "cudaMallocAsync": min(fp["cudaMallocAsync"]),
+                  "note": "driver calls on a shared host scatter by 2-3 x from one pass to the next whatever precedes them"}
     c.torch.cuda.synchronize()
     c.torch.cuda.empty_cache()
     # torch routes, each in a fresh process (the pluggable allocator has to be installed before the first allocation);
